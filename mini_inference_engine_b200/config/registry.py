@@ -6,6 +6,7 @@ from __future__ import annotations
 
 from .getizen_config import GetizenConfig
 from .kebudra_config import KebudraConfig
+from .serotar_config import SerotarConfig
 from .model_config import ConfigError, LlamaConfig, read_config_json
 
 _ARCHITECTURES: dict[str, type] = {}
@@ -42,6 +43,7 @@ def load_config(path_or_dict):
 register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("Getizen", GetizenConfig)
 register_architecture("Kebudra", KebudraConfig)
+register_architecture("Serotar", SerotarConfig)
 
 
 def preset_names() -> list[str]:

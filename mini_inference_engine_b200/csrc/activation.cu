@@ -223,3 +223,77 @@ extern "C" int mie_sigmoid_gate(const void* attn, const void* g, long long g_str
         return launch_kernel(sigmoid_gate_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)attn, (const bf16*)g, (int64_t)g_stride, (bf16*)out, total, H, Dv, DP);
     return MIE_ERR_BAD_ARG;
 }
+
+// xIELU, an activation with two constants: for z > 0 a quadratic arm, ap z^2 + z / 2; for z <= 0 an exponential arm,
+// an (exp(z) - 1 - z) + z / 2.  Both arms have slope 1/2 at 0.  The caller derives ap and an from the learned numbers.
+// Computed in float32 and rounded once.
+__device__ __forceinline__ float xielu_f(float z, float ap, float an) {
+    return z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(an, expm1f(z) - z, 0.5f * z);
+}
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t total, float ap, float an) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x)
+        out[idx] = from_f32<T>(xielu_f(to_f32<T>(x[idx]), ap, an));
+}
+__global__ void xielu_bf16x8_kernel(const bf16* __restrict__ x, bf16* __restrict__ out, int64_t total8, float ap, float an) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
+        uint4 u = *reinterpret_cast<const uint4*>(x + idx * 8);
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h[j]);
+            h[j] = __floats2bfloat162_rn(xielu_f(f.x, ap, an), xielu_f(f.y, ap, an));
+        }
+        *reinterpret_cast<uint4*>(out + idx * 8) = u;
+    }
+}
+
+extern "C" int mie_xielu(const void* x, void* out, int act_tag, long long total, float ap, float an, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int threads = 256;
+    if (act_tag == MIE_BF16 && total % 8 == 0 && (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+        int64_t blocks8 = (total / 8 + threads - 1) / threads;
+        if (blocks8 > device_sm_count() * 16) blocks8 = device_sm_count() * 16;
+        return launch_kernel(xielu_bf16x8_kernel, dim3((int)blocks8), dim3(threads), 0, stream, (const bf16*)x, (bf16*)out, (int64_t)(total / 8), ap, an);
+    }
+    int64_t blocks = (total + threads - 1) / threads;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    if (act_tag == MIE_F32)
+        return launch_kernel(xielu_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)x, (float*)out, (int64_t)total, ap, an);
+    else if (act_tag == MIE_BF16)
+        return launch_kernel(xielu_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)x, (bf16*)out, (int64_t)total, ap, an);
+    return MIE_ERR_BAD_ARG;
+}
+
+// A gate on rows gathered from a per-token table: out[t, d] = gelu_tanh(g[t, d]) * table[ids[t], first + d] for d < n, where a
+// table row has `table_width` entries.  ids are vocabulary entries (already resolved); one outside [0, vocab) gives zeros.
+template <typename T>
+__global__ void gelu_gate_rows_kernel(const T* __restrict__ g, const T* __restrict__ table, const int* __restrict__ ids,
+                                      T* __restrict__ out, int64_t total, int n, int table_width, int first, int vocab) {
+    pdl_enter();
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / n;
+        const int d = (int)(idx - t * n);
+        const int id = ids[t];
+        const float z = to_f32<T>(g[idx]);
+        const float e = id >= 0 && id < vocab ? to_f32<T>(table[(int64_t)id * table_width + first + d]) : 0.f;
+        out[idx] = from_f32<T>(0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))) * e);
+    }
+}
+
+extern "C" int mie_gelu_gate_rows(const void* g, const void* table, const int* ids, void* out, int act_tag, int num_tokens, int n,
+                                  int table_width, int first, int vocab, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (n <= 0 || first < 0 || first + n > table_width || vocab <= 0) return MIE_ERR_BAD_ARG;
+    const int64_t total = (int64_t)num_tokens * n;
+    const int threads = 256;
+    int64_t blocks = (total + threads - 1) / threads;
+    if (blocks > device_sm_count() * 16) blocks = device_sm_count() * 16;
+    if (act_tag == MIE_F32)
+        return launch_kernel(gelu_gate_rows_kernel<float>, dim3((int)blocks), dim3(threads), 0, stream, (const float*)g, (const float*)table, ids, (float*)out, total, n, table_width, first, vocab);
+    else if (act_tag == MIE_BF16)
+        return launch_kernel(gelu_gate_rows_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)g, (const bf16*)table, ids, (bf16*)out, total, n, table_width, first, vocab);
+    return MIE_ERR_BAD_ARG;
+}

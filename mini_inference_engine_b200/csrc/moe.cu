@@ -18,7 +18,78 @@
 //              product over rows sorted by expert): sort gives every (token, expert) pair its place among its expert's
 //              rows and the experts' row ranges; gather copies the tokens' inputs to those places; act_rows applies
 //              weight f(.) row by row; combine adds a token's rows up in float32, the pairs in order.
+//
+// A second routing rule (RouteRule.mode 1) and gated experts: scores s = softmax(z) over ALL router outputs; the choice is by
+// s + correction (optional), limited to the experts of the `keep` best of `groups` equal groups of neighbours (a group's value is
+// its largest choice score; the other groups count as minus infinity); the weights are the chosen s, not renormalized.  Router
+// outputs from `real` on are identity experts: no matrices, output = input; the expert kernels skip them and `rest[t]` receives
+// the sum of their weights for the caller to add rest[t] * x[t].  A gated expert is down(silu(gate x) * (up x)) with the stacked
+// matrix [expert 0: gate F rows, up F rows | expert 1: ...].
 #include "common.cuh"
+
+struct RouteRule {
+    int mode;                    // 0: the largest logits, softmax over the chosen; 1: softmax over all, see above
+    const float* correction;     // [outputs] added for the choice only (mode 1), or null
+    int groups, keep;            // groups <= 1 or keep >= groups: no limit
+    int real;                    // router outputs below this have matrices; the others are identity experts
+    float* rest;                 // [tokens] sum of the chosen identity experts' weights, or null
+};
+
+// Mode 1 for one token.  `ready`: zt already holds softmax scores (made by the block together); else logits.
+__device__ __forceinline__ void route_scored(const float* zt, int* ids, float* wts, int n, int top, const RouteRule& rr, bool ready,
+                                             float* rest) {
+    float m = 0.f, inv = 1.f;
+    if (!ready) {
+        m = -INFINITY;
+        for (int e = 0; e < n; ++e) m = fmaxf(m, zt[e]);
+        float sum = 0.f;
+        for (int e = 0; e < n; ++e) sum += expf(zt[e] - m);
+        inv = 1.0f / sum;
+    }
+    auto score = [&](int e) { return ready ? zt[e] : expf(zt[e] - m) * inv; };
+    auto choice = [&](int e) { return rr.correction ? score(e) + rr.correction[e] : score(e); };
+    unsigned long long allowed = ~0ull;
+    const int per = rr.groups > 1 ? n / rr.groups : n;
+    if (rr.groups > 1 && rr.keep < rr.groups) {
+        allowed = 0ull;
+        float prev_v = INFINITY;
+        int prev_g = -1;
+        for (int k = 0; k < rr.keep; ++k) {
+            float best = -INFINITY;
+            int bg = -1;
+            for (int g = 0; g < rr.groups; ++g) {
+                float v = -INFINITY;
+                for (int e = g * per; e < (g + 1) * per; ++e) v = fmaxf(v, choice(e));
+                const bool after_prev = v < prev_v || (v == prev_v && g > prev_g);
+                if (after_prev && (bg < 0 || v > best)) { best = v; bg = g; }
+            }
+            if (bg < 0) break;
+            allowed |= 1ull << bg;
+            prev_v = best;
+            prev_g = bg;
+        }
+    }
+    float prev_v = INFINITY, idw = 0.f;
+    int prev_i = -1;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int bi = -1;
+        for (int e = 0; e < n; ++e) {
+            if (!((allowed >> (rr.groups > 1 ? e / per : 0)) & 1ull)) continue;
+            const float v = choice(e);
+            const bool after_prev = v < prev_v || (v == prev_v && e > prev_i);
+            if (after_prev && (bi < 0 || v > best)) { best = v; bi = e; }
+        }
+        float w = 0.f;
+        if (bi < 0) bi = 0; else w = score(bi);               // scores that are not numbers: keep the ids in range, weight 0
+        ids[k] = bi;
+        wts[k] = w;
+        if (bi >= rr.real) idw += w;
+        prev_v = best;
+        prev_i = bi;
+    }
+    if (rest) *rest = idw;
+}
 
 // The `top` largest of zt[0 .. E) in order (ties: the lower index first) and the softmax over them.
 __device__ __forceinline__ void route_one(const float* zt, int* ids, float* wts, int E, int top) {
@@ -45,12 +116,23 @@ __device__ __forceinline__ void route_one(const float* zt, int* ids, float* wts,
     for (int k = 0; k < top; ++k) wts[k] /= sum;
 }
 
+__device__ __forceinline__ void route_by_rule(const float* zt, int* ids, float* wts, int E, int top, const RouteRule& rr, bool ready,
+                                              int64_t t) {
+    if (rr.mode == 1) { route_scored(zt, ids, wts, E, top, rr, ready, rr.rest ? rr.rest + t : nullptr); return; }
+    route_one(zt, ids, wts, E, top);
+    if (rr.rest) {
+        float idw = 0.f;
+        for (int k = 0; k < top; ++k) if (ids[k] >= rr.real) idw += wts[k];
+        rr.rest[t] = idw;
+    }
+}
+
 __global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ ids, float* __restrict__ wts, int num_tokens, int E,
-                                 int top) {
+                                 int top, RouteRule rr) {
     pdl_enter();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= num_tokens) return;
-    route_one(z + (int64_t)t * E, ids + (int64_t)t * top, wts + (int64_t)t * top, E, top);
+    route_by_rule(z + (int64_t)t * E, ids + (int64_t)t * top, wts + (int64_t)t * top, E, top, rr, false, t);
 }
 
 #define ROUTER_TOKENS 8      // tokens a block: the router's matrix is read once for all of them
@@ -59,7 +141,7 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ 
 // all of them (the expert's row is read once), then a thread per token chooses.  `logits` (optional) receives z.
 template <typename TA>
 __global__ void moe_router_kernel(const TA* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
-                                  float* __restrict__ logits, int num_tokens, int h, int E, int top, int tpb) {
+                                  float* __restrict__ logits, int num_tokens, int h, int E, int top, int tpb, RouteRule rr) {
     extern __shared__ __align__(16) float rs[];               // x [tpb, h], then z [tpb, E]
     float* z = rs + (size_t)tpb * h;
     pdl_enter();
@@ -109,8 +191,23 @@ __global__ void moe_router_kernel(const TA* __restrict__ x, const float* __restr
     __syncthreads();
     if (logits)
         for (int c = threadIdx.x; c < nt * E; c += blockDim.x) logits[(int64_t)t0 * E + c] = z[c];
+    if (rr.mode == 1) {                          // the scores of all outputs, a warp per token: the choice then reads them
+        __syncthreads();
+        for (int i = warp; i < nt; i += nw) {
+            float m = -INFINITY;
+            for (int e = lane; e < E; e += 32) m = fmaxf(m, z[i * E + e]);
+            m = warp_max(m);
+            float sum = 0.f;
+            for (int e = lane; e < E; e += 32) { const float p = expf(z[i * E + e] - m); z[i * E + e] = p; sum += p; }
+            sum = warp_sum(sum);
+            __syncwarp();
+            for (int e = lane; e < E; e += 32) z[i * E + e] /= sum;
+        }
+        __syncthreads();
+    }
     if (threadIdx.x < nt)
-        route_one(z + threadIdx.x * E, ids + (int64_t)(t0 + threadIdx.x) * top, wts + (int64_t)(t0 + threadIdx.x) * top, E, top);
+        route_by_rule(z + threadIdx.x * E, ids + (int64_t)(t0 + threadIdx.x) * top, wts + (int64_t)(t0 + threadIdx.x) * top, E, top, rr,
+                      rr.mode == 1, t0 + threadIdx.x);
 }
 
 __device__ __forceinline__ float expert_act(float x, int kind) {
@@ -164,19 +261,27 @@ __device__ __forceinline__ float row_dot(const TW* __restrict__ row, const float
 
 template <typename TA, typename TW>
 __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restrict__ w_up, const int* __restrict__ ids,
-                                    const float* __restrict__ wts, TA* __restrict__ hid, int h, int F, int top, int kind) {
+                                    const float* __restrict__ wts, TA* __restrict__ hid, int h, int E, int F, int top, int kind,
+                                    int gated) {
     extern __shared__ __align__(16) float xs[];               // the token's input, float32
     pdl_enter();
     const int pair = blockIdx.x, t = pair / top;
     const int e = ids[pair];
     const float weight = wts[pair];
+    if (e >= E) return;                                        // an identity expert: the down kernel skips the pair
     for (int c = threadIdx.x; c < h; c += blockDim.x) xs[c] = to_f32<TA>(x[(int64_t)t * h + c]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int f0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP;
     for (int f = f0; f < min(f0 + MOE_ROWS_PER_WARP, F); ++f) {
-        const float d = row_dot<TW>(w_up + ((int64_t)e * F + f) * h, xs, h, lane);
-        if (lane == 0) hid[(int64_t)pair * F + f] = from_f32<TA>(weight * expert_act(d, kind));
+        float v;
+        if (gated) {
+            const float g = row_dot<TW>(w_up + ((int64_t)e * 2 * F + f) * h, xs, h, lane);
+            v = expert_act(g, kind) * row_dot<TW>(w_up + ((int64_t)e * 2 * F + F + f) * h, xs, h, lane);
+        } else {
+            v = expert_act(row_dot<TW>(w_up + ((int64_t)e * F + f) * h, xs, h, lane), kind);
+        }
+        if (lane == 0) hid[(int64_t)pair * F + f] = from_f32<TA>(weight * v);
     }
 }
 
@@ -186,21 +291,24 @@ __global__ void moe_pairs_down_kernel(const TA* __restrict__ hid, const TW* __re
     extern __shared__ __align__(16) float hs[];               // the token's `top` hidden rows, float32 [top, F]
     pdl_enter();
     const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < top * F; c += blockDim.x) hs[c] = to_f32<TA>(hid[(int64_t)t * top * F + c]);
+    for (int c = threadIdx.x; c < top * F; c += blockDim.x)
+        hs[c] = ids[t * top + c / F] < E ? to_f32<TA>(hid[(int64_t)t * top * F + c]) : 0.f;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int n0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP;
     for (int n = n0; n < min(n0 + MOE_ROWS_PER_WARP, h); ++n) {
         float acc = 0.f;
-        for (int k = 0; k < top; ++k)
-            acc += row_dot<TW>(w_down + (int64_t)n * E * F + (int64_t)ids[t * top + k] * F, hs + k * F, F, lane);
+        for (int k = 0; k < top; ++k) {
+            const int e = ids[t * top + k];
+            if (e < E) acc += row_dot<TW>(w_down + (int64_t)n * E * F + (int64_t)e * F, hs + k * F, F, lane);
+        }
         if (lane == 0) out[(int64_t)t * h + n] = acc;
     }
 }
 
 template <typename TA, typename TW>
 static int launch_pairs(const void* x, const void* w_up, const void* w_down, const int* ids, const float* wts, void* hid, float* out,
-                        int T, int h, int E, int F, int top, int kind, cudaStream_t stream) {
+                        int T, int h, int E, int F, int top, int kind, int gated, cudaStream_t stream) {
     const int threads = 256, rows = (threads / 32) * MOE_ROWS_PER_WARP;
     const size_t smem_up = (size_t)h * sizeof(float), smem_down = (size_t)top * F * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(moe_pairs_up_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
@@ -208,7 +316,7 @@ static int launch_pairs(const void* x, const void* w_up, const void* w_down, con
     e = cudaFuncSetAttribute(moe_pairs_down_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     if (e != cudaSuccess) return (int)e;
     int rc = launch_kernel(moe_pairs_up_kernel<TA, TW>, dim3(T * top, (F + rows - 1) / rows), dim3(threads), smem_up, stream, (const TA*)x,
-                           (const TW*)w_up, ids, wts, (TA*)hid, h, F, top, kind);
+                           (const TW*)w_up, ids, wts, (TA*)hid, h, E, F, top, kind, gated);
     if (rc != 0) return rc;
     return launch_kernel(moe_pairs_down_kernel<TA, TW>, dim3(T, (h + rows - 1) / rows), dim3(threads), smem_down, stream, (const TA*)hid,
                          (const TW*)w_down, ids, out, h, E, F, top);
@@ -221,16 +329,17 @@ extern "C" int mie_moe_pairs_fit(int h, int F, int top) {
 
 // x [T, h] and hid [T * top, F] in the activation type (act_tag), w_up [E * F, h] and w_down [h, E * F] in w_tag, out [T, h] float32.
 extern "C" int mie_moe_pairs(const void* x, int act_tag, const void* w_up, const void* w_down, int w_tag, const int* ids, const float* wts,
-                             void* hid, float* out, int num_tokens, int h, int E, int F, int top, int kind, cudaStream_t stream) {
+                             void* hid, float* out, int num_tokens, int h, int E, int F, int top, int kind, int gated,
+                             cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    if (E <= 0 || top <= 0 || top > E || kind < 0 || kind > 2 || !mie_moe_pairs_fit(h, F, top)) return MIE_ERR_BAD_ARG;
+    if (E <= 0 || top <= 0 || kind < 0 || kind > 2 || !mie_moe_pairs_fit(h, F, top)) return MIE_ERR_BAD_ARG;
     if (((reinterpret_cast<uintptr_t>(w_up) | reinterpret_cast<uintptr_t>(w_down)) & 15) != 0) return MIE_ERR_BAD_ARG;
     if (act_tag == MIE_F32 && w_tag == MIE_F32)
-        return launch_pairs<float, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
+        return launch_pairs<float, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, stream);
     if (act_tag == MIE_BF16 && w_tag == MIE_BF16)
-        return launch_pairs<bf16, bf16>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
+        return launch_pairs<bf16, bf16>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, stream);
     if (act_tag == MIE_BF16 && w_tag == MIE_F32)
-        return launch_pairs<bf16, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, stream);
+        return launch_pairs<bf16, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, stream);
     return MIE_ERR_BAD_ARG;
 }
 
@@ -302,12 +411,13 @@ __global__ void moe_act_rows_bf16x8_kernel(bf16* __restrict__ up, const float* _
 // out[t, :] = sum over k < top of rows[place[t * top + k], :], float32, k in order.
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __restrict__ place, float* __restrict__ out, int num_tokens,
-                                   int h, int top) {
+                                   int h, int top, const int* __restrict__ ids, int real) {
     pdl_enter();
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < (int64_t)num_tokens * h; idx += (int64_t)gridDim.x * blockDim.x) {
         const int t = (int)(idx / h), c = (int)(idx - (int64_t)t * h);
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc += to_f32<T>(rows[(int64_t)place[t * top + k] * h + c]);
+        for (int k = 0; k < top; ++k)
+            if (!ids || ids[t * top + k] < real) acc += to_f32<T>(rows[(int64_t)place[t * top + k] * h + c]);
         out[idx] = acc;
     }
 }
@@ -355,23 +465,37 @@ extern "C" int mie_moe_act_rows(void* up, const float* row_weight, int tag, int 
     return MIE_ERR_BAD_ARG;
 }
 
-extern "C" int mie_moe_combine(const void* rows, const int* place, float* out, int tag, int num_tokens, int h, int top, cudaStream_t stream) {
+// ids / real (optional): pairs whose expert id is `real` or more have no row to add (identity experts).
+extern "C" int mie_moe_combine(const void* rows, const int* place, float* out, int tag, int num_tokens, int h, int top, const int* ids,
+                               int real, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (h <= 0 || top <= 0) return MIE_ERR_BAD_ARG;
     const int64_t items = (int64_t)num_tokens * h;
     if (tag == MIE_F32)
         return launch_kernel(moe_combine_kernel<float>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const float*)rows, place, out,
-                             num_tokens, h, top);
+                             num_tokens, h, top, ids, real);
     else if (tag == MIE_BF16)
         return launch_kernel(moe_combine_kernel<bf16>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const bf16*)rows, place, out,
-                             num_tokens, h, top);
+                             num_tokens, h, top, ids, real);
     return MIE_ERR_BAD_ARG;
 }
 
+static bool rule_ok(const RouteRule& rr, int E, int top) {
+    if (rr.mode != 0 && rr.mode != 1) return false;
+    if (rr.real < 0 || rr.real > E) return false;
+    if (rr.mode == 1 && rr.groups > 1) {
+        if (rr.groups > 64 || E % rr.groups || rr.keep < 1 || (rr.keep < rr.groups && top > rr.keep * (E / rr.groups))) return false;
+    }
+    return true;
+}
+
 extern "C" int mie_moe_router(const void* x, int tag, const float* w, int* ids, float* wts, float* logits, int num_tokens, int h, int E,
-                              int top, cudaStream_t stream) {
+                              int top, int mode, const float* correction, int groups, int keep, int real, float* rest,
+                              cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || h <= 0) return MIE_ERR_BAD_ARG;
+    const RouteRule rr{mode, correction, groups, keep, real, rest};
+    if (!rule_ok(rr, E, top)) return MIE_ERR_BAD_ARG;
     int tpb = ROUTER_TOKENS;                                   // fewer where the tokens' inputs would not fit in 96 KB ...
     while (tpb > 1 && (size_t)tpb * (h + E) * sizeof(float) > 96 * 1024) tpb >>= 1;
     while (tpb > 1 && (num_tokens + tpb - 1) / tpb < device_sm_count()) tpb >>= 1;      // ... or would leave SMs without a block
@@ -381,20 +505,23 @@ extern "C" int mie_moe_router(const void* x, int tag, const float* w, int* ids, 
     cudaError_t e;
     if (tag == MIE_F32) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_kernel(moe_router_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb);
+        return launch_kernel(moe_router_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb, rr);
     } else if (tag == MIE_BF16) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_kernel(moe_router_kernel<bf16>, dim3(blocks), dim3(threads), smem, stream, (const bf16*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb);
+        return launch_kernel(moe_router_kernel<bf16>, dim3(blocks), dim3(threads), smem, stream, (const bf16*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb, rr);
     }
     return MIE_ERR_BAD_ARG;
 }
 
-extern "C" int mie_moe_route(const float* z, int* ids, float* wts, int num_tokens, int E, int top, cudaStream_t stream) {
+extern "C" int mie_moe_route(const float* z, int* ids, float* wts, int num_tokens, int E, int top, int mode, const float* correction,
+                             int groups, int keep, int real, float* rest, cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E) return MIE_ERR_BAD_ARG;
+    const RouteRule rr{mode, correction, groups, keep, real, rest};
+    if (!rule_ok(rr, E, top)) return MIE_ERR_BAD_ARG;
     const int threads = 64;
     return launch_kernel(moe_route_kernel, dim3((num_tokens + threads - 1) / threads), dim3(threads), 0, stream, z, ids, wts, num_tokens,
-                         E, top);
+                         E, top, rr);
 }
 
 // The same, eight bfloat16 a thread; an expert the token did not choose is written as zeros without reading its inputs.
@@ -443,5 +570,72 @@ extern "C" int mie_moe_dense_act(const void* up, const int* ids, const float* wt
     else if (tag == MIE_BF16)
         return launch_kernel(moe_dense_act_kernel<bf16>, dim3((int)blocks), dim3(threads), 0, stream, (const bf16*)up, ids, wts,
                              (bf16*)act, total, E, F, top, kind);
+    return MIE_ERR_BAD_ARG;
+}
+
+// Gated experts, the activation between the two products.  rows form: hid[r, f] = row_weight[r] f(gu[r, f]) gu[r, F + f] with
+// gu [R, 2F] (the sorted pairs' rows); wide form: act[t, e, f] = weight(t, e) f(gu[t, e, f]) gu[t, e, F + f] for a chosen
+// expert and 0 for the others, with gu [T, E, 2F].  `per_row` = 1 for the rows form (E = 1, the weight by row).
+template <typename T>
+__global__ void moe_glu_kernel(const T* __restrict__ gu, const int* __restrict__ ids, const float* __restrict__ wts, T* __restrict__ act,
+                               int64_t total, int E, int F, int top, int kind, int per_row) {
+    pdl_enter();
+    const int64_t EF = (int64_t)E * F;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / EF;
+        const int e = (int)((idx - t * EF) / F), f = (int)(idx - t * EF - (int64_t)e * F);
+        float w = 0.f;
+        if (per_row) w = wts[t];
+        else
+            for (int k = 0; k < top; ++k)
+                if (ids[t * top + k] == e) w = wts[t * top + k];
+        const int64_t at = (t * E + e) * 2 * F + f;
+        act[idx] = from_f32<T>(w != 0.f ? w * expert_act(to_f32<T>(gu[at]), kind) * to_f32<T>(gu[at + F]) : 0.f);
+    }
+}
+__global__ void moe_glu_bf16x8_kernel(const bf16* __restrict__ gu, const int* __restrict__ ids, const float* __restrict__ wts,
+                                      bf16* __restrict__ act, int64_t total8, int E, int F8, int top, int kind, int per_row) {
+    pdl_enter();
+    const int64_t EF8 = (int64_t)E * F8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = idx / EF8;
+        const int e = (int)((idx - t * EF8) / F8), f8 = (int)(idx - t * EF8 - (int64_t)e * F8);
+        float w = 0.f;
+        if (per_row) w = wts[t];
+        else
+            for (int k = 0; k < top; ++k)
+                if (ids[t * top + k] == e) w = wts[t * top + k];
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (w != 0.f) {
+            const bf16* at = gu + ((t * E + e) * 2 * F8 + f8) * 8;
+            const uint4 g = *reinterpret_cast<const uint4*>(at), u = *reinterpret_cast<const uint4*>(at + (int64_t)F8 * 8);
+            const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&g);
+            const __nv_bfloat162* hu = reinterpret_cast<const __nv_bfloat162*>(&u);
+            __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 a = __bfloat1622float2(hg[i]), b = __bfloat1622float2(hu[i]);
+                ho[i] = __floats2bfloat162_rn(w * expert_act(a.x, kind) * b.x, w * expert_act(a.y, kind) * b.y);
+            }
+        }
+        *reinterpret_cast<uint4*>(act + idx * 8) = o;
+    }
+}
+
+// gu [rows, E, 2F] -> act [rows, E, F]; per_row: E must be 1 and wts holds one weight a row (ids unused).
+extern "C" int mie_moe_glu(const void* gu, const int* ids, const float* wts, void* act, int tag, int rows, int E, int F, int top, int kind,
+                           int per_row, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (E <= 0 || F <= 0 || kind < 0 || kind > 2 || (per_row ? E != 1 : (top <= 0 || !ids))) return MIE_ERR_BAD_ARG;
+    const int64_t total = (int64_t)rows * E * F;
+    if (tag == MIE_BF16 && F % 8 == 0 && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(act)) & 15) == 0)
+        return launch_kernel(moe_glu_bf16x8_kernel, dim3(capped_blocks(total / 8, 256)), dim3(256), 0, stream, (const bf16*)gu, ids, wts,
+                             (bf16*)act, total / 8, E, F / 8, top, kind, per_row);
+    if (tag == MIE_F32)
+        return launch_kernel(moe_glu_kernel<float>, dim3(capped_blocks(total, 256)), dim3(256), 0, stream, (const float*)gu, ids, wts,
+                             (float*)act, total, E, F, top, kind, per_row);
+    else if (tag == MIE_BF16)
+        return launch_kernel(moe_glu_kernel<bf16>, dim3(capped_blocks(total, 256)), dim3(256), 0, stream, (const bf16*)gu, ids, wts,
+                             (bf16*)act, total, E, F, top, kind, per_row);
     return MIE_ERR_BAD_ARG;
 }

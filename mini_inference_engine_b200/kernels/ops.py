@@ -142,6 +142,91 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, feedbac
     return out
 
 
+def pair_embedding(table: torch.Tensor, pair_table, ctx, last_token: torch.Tensor, out: torch.Tensor, *, scale: float, buckets: int = 0,
+                   mul_prev: int = 0, mul_cur: int = 0, first=None, act=None, resolved=None) -> torch.Tensor:
+    """out[t] = table[id] * scale + pair_table[(prev * mul_prev + id * mul_cur) mod buckets] (row ``buckets`` at a sequence's first
+    token; no second table: the first term alone), float32.  The token in front of a batch row's first token is the
+    sequence's ``last_token`` state (int32 [slots + 1, 1], indexed by ``ctx.state_slots``), which is left holding the row's
+    last token.  ``first`` (float32) and ``act`` (bfloat16) receive copies of ``out``; ``resolved`` (int32 [T]) the token
+    ids with fed-back tokens replaced."""
+    V, h = table.shape
+    T = ctx.num_tokens
+    fb = ctx.token_feedback
+    _need(table.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, h), "out must be float32 [T, hidden]")
+    if pair_table is not None:
+        _need(pair_table.is_contiguous() and pair_table.shape == (buckets + 1, h) and pair_table.dtype == table.dtype,
+              "the pair table must be [buckets + 1, hidden] in the embedding's type")
+    _need(last_token.dtype == torch.int32 and last_token.is_contiguous(), "the last-token state must be contiguous int32")
+    for t, name in ((first, "first"), (act, "act")):
+        if t is not None:
+            _need(t.is_contiguous() and t.numel() == T * h and t.dtype == (torch.float32 if name == "first" else torch.bfloat16),
+                  f"{name} must be contiguous [T, hidden]")
+    if resolved is not None:
+        _i32(resolved, "resolved")
+    if fb is not None:
+        _i32(fb, "feedback")
+    lib = load("embedding")
+    _check(lib.mie_pair_embedding(_ptr(table), _ptr(pair_table), tag(table), _ptr(ctx.token_ids), _ptr(fb), _ptr(ctx.positions),
+                                  _ptr(ctx.token_row), _ptr(ctx.row_q_start), _ptr(ctx.row_q_len), _ptr(ctx.state_slots),
+                                  _ptr(last_token), _ptr(out), _ptr(first), _ptr(act), _ptr(resolved), T, h, V,
+                                  fb.numel() if fb is not None else 0, ctypes.c_float(scale), int(buckets), ctypes.c_longlong(mul_prev),
+                                  ctypes.c_longlong(mul_cur), ctx.num_rows, last_token.shape[0], _stream()), "pair_embedding")
+    return out
+
+
+def normed_add(res: torch.Tensor, addends=(), *, scaled=None, gain=None, vec=None, eps: float = 0.0, act=None, history=None,
+               slot: int = 0, coef=None) -> torch.Tensor:
+    """res += y / sqrt(mean(y^2) + eps) * gain * vec with y the sum of ``addends`` (up to three [T, W] tensors) and of
+    ``scaled`` = (h [T, W], row_scale float32 [T]) as row_scale[t] * h[t]; ``gain`` one float32 on the device, ``vec`` float32
+    [W], both optional.  With ``history`` (float32 [slots, T, W]) the new stream is stored as entry ``slot`` and ``res``
+    becomes sum over j <= slot of coef[j] * history[j].  ``act`` (bfloat16 [T, W]) receives the rounded result.  Without
+    addends nothing is added."""
+    T, W = res.shape
+    _need(res.dtype == torch.float32 and res.is_contiguous(), "the stream must be contiguous float32")
+    addends = [a for a in addends if a is not None]
+    _need(len(addends) <= 3, "at most three addends")
+    for a in addends + ([scaled[0]] if scaled is not None else []):
+        _need(a.is_contiguous() and a.shape == (T, W), "an addend must be contiguous [T, W]")
+    if scaled is not None:
+        _f32(scaled[1], "row scale", T)
+    if gain is not None:
+        _f32(gain, "gain", 1)
+    if vec is not None:
+        _f32(vec, "scale vector", W)
+    if act is not None:
+        _need(act.dtype == torch.bfloat16 and act.is_contiguous() and act.shape == (T, W), "act must be bfloat16 [T, W]")
+    if history is not None:
+        _need(history.dtype == torch.float32 and history.is_contiguous() and history.shape[1:] == (T, W) and 0 <= slot < history.shape[0],
+              "history must be float32 [slots, T, W]")
+        _f32(coef, "depth coefficients", slot + 1)
+    pa = [(_ptr(a), tag(a)) for a in addends] + [(ctypes.c_void_p(0), 0)] * (3 - len(addends))
+    lib = load("stream_update")
+    _check(lib.mie_normed_add(_ptr(res), pa[0][0], pa[0][1], pa[1][0], pa[1][1], pa[2][0], pa[2][1], len(addends),
+                              _ptr(scaled[0]) if scaled is not None else ctypes.c_void_p(0), tag(scaled[0]) if scaled is not None else 0,
+                              _ptr(scaled[1]) if scaled is not None else ctypes.c_void_p(0), _ptr(gain), _ptr(vec), ctypes.c_float(eps),
+                              _ptr(act), _ptr(history), ctypes.c_longlong(T * W), int(slot), _ptr(coef), T, W, _stream()), "normed_add")
+    return res
+
+
+def xielu(x: torch.Tensor, out: torch.Tensor, ap: float, an: float) -> torch.Tensor:
+    """out = ap x^2 + x / 2 where x > 0, an (exp(x) - 1 - x) + x / 2 elsewhere."""
+    _need(x.is_contiguous() and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype, "xielu: contiguous tensors of one shape and type")
+    _check(load("activation").mie_xielu(_ptr(x), _ptr(out), tag(x), ctypes.c_longlong(x.numel()), ctypes.c_float(ap), ctypes.c_float(an),
+                                        _stream()), "xielu")
+    return out
+
+
+def gelu_gate_rows(g: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, first: int, out: torch.Tensor) -> torch.Tensor:
+    """out[t, d] = gelu_tanh(g[t, d]) * table[ids[t], first + d]."""
+    T, n = g.shape
+    _need(g.is_contiguous() and out.is_contiguous() and out.shape == g.shape and out.dtype == g.dtype == table.dtype and table.is_contiguous(),
+          "gate rows: contiguous tensors of one type")
+    _i32(ids, "ids")
+    _check(load("activation").mie_gelu_gate_rows(_ptr(g), _ptr(table), _ptr(ids), _ptr(out), tag(g), T, n, table.shape[1], int(first),
+                                                 table.shape[0], _stream()), "gelu_gate_rows")
+    return out
+
+
 # --------------------------------------------------------------------------- norm
 
 def add_rmsnorm(delta, res: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -938,21 +1023,48 @@ def head_norm_gate(o: torch.Tensor, gate, weight, out: torch.Tensor, num_heads: 
 EXPERT_ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
 
 
-def moe_route(logits: torch.Tensor, top: int):
-    """The ``top`` largest of each row of float32 ``logits`` [T, E] (ties: lower index first) and the softmax over them:
-    (ids int32 [T, top], weights float32 [T, top])."""
+class RouteRule:
+    """How a router turns its outputs into a choice.  ``score`` "top_softmax": the ``top`` largest logits, weights = softmax
+    over those.  ``score`` "softmax": scores = softmax over all outputs; the choice is by score + ``correction`` (float32
+    [outputs], optional), limited to the ``keep`` best of ``groups`` equal groups of neighbouring outputs (a group's value is
+    its largest choice score); weights = the chosen scores, not renormalized.  Outputs from ``real`` on (None: there are
+    none) are identity experts; the sum of their chosen weights is returned per token."""
+
+    def __init__(self, score: str = "top_softmax", correction=None, groups: int = 1, keep: int = 1, real: int | None = None):
+        _need(score in ("top_softmax", "softmax"), f"router score {score!r}; one of top_softmax, softmax")
+        if correction is not None:
+            _f32(correction, "router correction")
+        self.mode, self.correction, self.groups, self.keep, self.real = int(score == "softmax"), correction, int(groups), int(keep), real
+
+    def args(self, outputs: int, tokens: int, device):
+        """(ctypes arguments behind ``top``, the per-token rest weights or None)."""
+        _need(self.correction is None or self.correction.numel() == outputs, "one correction per router output")
+        real = outputs if self.real is None else int(self.real)
+        rest = torch.empty(tokens, dtype=torch.float32, device=device) if real < outputs else None
+        return (self.mode, _ptr(self.correction), self.groups, self.keep, real, _ptr(rest)), rest
+
+
+_PLAIN_RULE = RouteRule()
+
+
+def moe_route(logits: torch.Tensor, top: int, rule: RouteRule | None = None):
+    """The choice of each row of float32 ``logits`` [T, outputs] under ``rule`` (default: the ``top`` largest, ties: lower index
+    first, softmax over them): (ids int32 [T, top], weights float32 [T, top]), and with a rule that has identity experts a
+    third value, float32 [T]: the sum of their weights."""
     T, E = logits.shape
     _f32(logits, "router logits")
     ids = torch.empty(T, top, dtype=torch.int32, device=logits.device)
     wts = torch.empty(T, top, dtype=torch.float32, device=logits.device)
+    extra, rest = (rule or _PLAIN_RULE).args(E, T, logits.device)
     lib = load("moe")
-    _check(lib.mie_moe_route(_ptr(logits), _ptr(ids), _ptr(wts), T, E, int(top), _stream()), "moe_route")
-    return ids, wts
+    _check(lib.mie_moe_route(_ptr(logits), _ptr(ids), _ptr(wts), T, E, int(top), *extra, _stream()), "moe_route")
+    return (ids, wts) if rule is None or rest is None else (ids, wts, rest)
 
 
-def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int, logits: torch.Tensor | None = None):
+def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int, logits: torch.Tensor | None = None, rule: RouteRule | None = None):
     """Router logits z = x w_router^T in float32 (``w_router`` float32 [E, h]; ``x`` widened) and the choice of ``moe_route`` in
-    one kernel: (ids int32 [T, top], weights float32 [T, top]); ``logits`` float32 [T, E], if given, receives z."""
+    one kernel: (ids int32 [T, top], weights float32 [T, top]) (and the identity experts' weights, as ``moe_route``);
+    ``logits`` float32 [T, E], if given, receives z."""
     T, h = x.shape
     E = w_router.shape[0]
     _need(x.is_contiguous() and w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape == (E, h),
@@ -961,9 +1073,10 @@ def moe_router(x: torch.Tensor, w_router: torch.Tensor, top: int, logits: torch.
         _need(logits.dtype == torch.float32 and logits.is_contiguous() and logits.shape == (T, E), "logits must be float32 [T, E]")
     ids = torch.empty(T, top, dtype=torch.int32, device=x.device)
     wts = torch.empty(T, top, dtype=torch.float32, device=x.device)
-    _check(load("moe").mie_moe_router(_ptr(x), tag(x), _ptr(w_router), _ptr(ids), _ptr(wts), _ptr(logits), T, h, E, int(top), _stream()),
-           "moe_router")
-    return ids, wts
+    extra, rest = (rule or _PLAIN_RULE).args(E, T, x.device)
+    _check(load("moe").mie_moe_router(_ptr(x), tag(x), _ptr(w_router), _ptr(ids), _ptr(wts), _ptr(logits), T, h, E, int(top), *extra,
+                                      _stream()), "moe_router")
+    return (ids, wts) if rule is None or rest is None else (ids, wts, rest)
 
 
 def moe_dense_act(up: torch.Tensor, ids, wts, act: torch.Tensor, num_experts: int, activation: str) -> torch.Tensor:
@@ -983,23 +1096,25 @@ def moe_pairs_fit(hidden: int, expert_size: int, top: int) -> bool:
 
 
 def moe_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids, wts, out: torch.Tensor, num_experts: int,
-              activation: str) -> torch.Tensor:
+              activation: str, gated: bool = False) -> torch.Tensor:
     """The routed experts for a handful of tokens: every (token, chosen expert) pair reads its expert's rows of the
     stacked matrices ``w_up`` [E * F, h] and ``w_down`` [h, E * F] and nothing else.  out [T, h] float32 = sum over the
-    token's pairs of weight * W_down[e] f(W_up[e] x)."""
+    token's pairs of weight * W_down[e] f(W_up[e] x).  ``gated``: ``w_up`` is [E * 2F, h], per expert F gate rows then F up rows,
+    and the hidden row is f(gate x) * (up x).  A pair whose id is ``num_experts`` or more (an identity expert) adds nothing."""
     T, h = x.shape
     top = ids.shape[1]
-    EF = w_up.shape[0]
+    EF = w_down.shape[1]
     F = EF // num_experts
-    _need(x.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and w_up.shape == (EF, h) and w_down.shape == (h, EF)
-          and w_up.dtype == w_down.dtype and F * num_experts == EF, "stacked expert matrices must be contiguous [E * F, h] and [h, E * F]")
+    _need(x.is_contiguous() and w_up.is_contiguous() and w_down.is_contiguous() and w_up.shape == ((2 if gated else 1) * EF, h)
+          and w_down.shape == (h, EF) and w_up.dtype == w_down.dtype and F * num_experts == EF,
+          "stacked expert matrices must be contiguous [E * F, h] ([E * 2F, h] gated) and [h, E * F]")
     _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, h), "out must be float32 [T, h]")
     _need(ids.dtype == torch.int32 and ids.is_contiguous() and wts.dtype == torch.float32 and wts.is_contiguous() and wts.shape == ids.shape,
           "ids int32 and weights float32 [T, top]")
     hid = torch.empty(T * top, F, dtype=x.dtype, device=x.device)
     lib = load("moe")
     _check(lib.mie_moe_pairs(_ptr(x), tag(x), _ptr(w_up), _ptr(w_down), tag(w_up), _ptr(ids), _ptr(wts), _ptr(hid), _ptr(out), T, h,
-                             int(num_experts), F, top, EXPERT_ACTIVATIONS[activation], _stream()), "moe_pairs")
+                             int(num_experts), F, top, EXPERT_ACTIVATIONS[activation], int(gated), _stream()), "moe_pairs")
     return out
 
 
@@ -1034,12 +1149,31 @@ def moe_act_rows(up: torch.Tensor, row_weight: torch.Tensor, activation: str) ->
     return up
 
 
-def moe_combine(rows: torch.Tensor, place: torch.Tensor, top: int, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum over k of rows[place[t * top + k]], float32."""
+def moe_combine(rows: torch.Tensor, place: torch.Tensor, top: int, out: torch.Tensor, ids=None, real: int = 0) -> torch.Tensor:
+    """out[t] = sum over k of rows[place[t * top + k]], float32; with ``ids`` [T, top], only the pairs whose id is below ``real``."""
     T, h = out.shape
     _need(rows.is_contiguous() and rows.shape == (T * top, h) and out.dtype == torch.float32 and out.is_contiguous(), "rows [T * top, h], out float32 [T, h]")
-    _check(load("moe").mie_moe_combine(_ptr(rows), _ptr(place), _ptr(out), tag(rows), T, h, int(top), _stream()), "moe_combine")
+    _check(load("moe").mie_moe_combine(_ptr(rows), _ptr(place), _ptr(out), tag(rows), T, h, int(top), _ptr(ids), int(real), _stream()),
+           "moe_combine")
     return out
+
+
+def moe_glu(gu: torch.Tensor, num_experts: int, activation: str, *, ids=None, wts=None, row_weight=None) -> torch.Tensor:
+    """The activation of gated experts.  With ``ids``/``wts`` [T, top] and ``gu`` [T, E * 2F] (per expert F gate then F up
+    entries): act [T, E * F] = weight f(gate) up for the experts a token chose, 0 for the others.  With ``row_weight`` [R] and
+    ``gu`` [R, 2F]: hid [R, F] = row_weight f(gate) up, row by row."""
+    R = gu.shape[0]
+    per_row = row_weight is not None
+    E = 1 if per_row else int(num_experts)
+    _need(gu.is_contiguous() and gu.shape[1] % (2 * E) == 0, "gate|up rows must be contiguous [rows, E * 2F]")
+    F = gu.shape[1] // (2 * E)
+    w = row_weight if per_row else wts
+    _need(w.dtype == torch.float32 and w.is_contiguous() and (w.numel() == R if per_row else (ids is not None and w.shape == ids.shape and ids.shape[0] == R)),
+          "float32 weights: one a row, or [T, top] beside int32 ids")
+    act = torch.empty(R, E * F, dtype=gu.dtype, device=gu.device)
+    _check(load("moe").mie_moe_glu(_ptr(gu), _ptr(ids), _ptr(w), _ptr(act), tag(gu), R, E, F, 0 if per_row else ids.shape[1],
+                                   EXPERT_ACTIVATIONS[activation], int(per_row), _stream()), "moe_glu")
+    return act
 
 
 def grouped_linear(rows: torch.Tensor, b: torch.Tensor, ends: torch.Tensor) -> torch.Tensor:

@@ -19,16 +19,20 @@ from ..parts.base import Runtime, StepContext, build_part, part_class
 from ..weights.loader import TensorSpec, check_and_bind
 
 
+EMBEDDING_CACHE = "embedding"      # the cache id of the embedding's own per-request state (layers use integers)
+
+
 def _layer_parts(layer_spec):
     """Builds the parts a layer's block class asks for (its ``roles``: role name -> part category)
     from the layer's description and hands them to the block by role name."""
     cls = part_class("block", layer_spec.block)
     roles = cls.roles
-    if set(roles) != set(layer_spec.parts):
+    optional = set(getattr(cls, "optional_roles", ()))
+    if not set(roles) - optional <= set(layer_spec.parts) <= set(roles):
         raise ValueError(f"block {layer_spec.block!r} is made of {', '.join(sorted(roles))}; the layer describes "
                          f"{', '.join(sorted(layer_spec.parts))}")
-    built = {role: build_part(roles[role], layer_spec.parts[role]) for role in roles}
-    return cls(**built, **layer_spec.params), [(layer_spec.parts[role].prefix, built[role]) for role in roles]
+    built = {role: build_part(roles[role], layer_spec.parts[role]) for role in roles if role in layer_spec.parts}
+    return cls(**built, **layer_spec.params), [(layer_spec.parts[role].prefix, built[role]) for role in built]
 
 
 class _Skeleton:
@@ -96,6 +100,10 @@ class DecoderModel:
             if e.cache in needs and needs[e.cache] != need:
                 raise ValueError(f"cache {e.cache} is used by layers with different needs: {needs[e.cache]} and {need}")
             needs[e.cache] = need
+        # an embedding may keep state per request too (what it must know of the tokens before a step); its cache id is a name
+        self._embedding_need = getattr(self.embedding, "cache_need", lambda: None)()
+        if self._embedding_need is not None:
+            needs[EMBEDDING_CACHE] = self._embedding_need
         first_writer = {}
         for e in self.run_order:
             if e.writes_cache:
@@ -111,6 +119,7 @@ class DecoderModel:
         self.storage = CacheStorage(self.cache_layout, num_pages, page_size, num_state_slots, self.rt.dtype,
                                     self.rt.device)
         self._caches = [self.storage.layer_cache(e.cache, e.writes_cache) for e in self.run_order]
+        self._embedding_cache = self.storage.layer_cache(EMBEDDING_CACHE) if self._embedding_need is not None else None
         return self.storage
 
     def weight_bytes(self) -> int:
@@ -136,7 +145,7 @@ class DecoderModel:
             return self._step(ctx)
 
     def _step(self, ctx: StepContext) -> torch.Tensor:
-        res = self.embedding.forward(ctx)
+        res = self.embedding.forward(ctx) if self._embedding_cache is None else self.embedding.forward(ctx, self._embedding_cache)
         delta = None
         if isinstance(res, tuple):                 # an embedding that hands on more than the stream (its value in the activation type)
             res, delta = res

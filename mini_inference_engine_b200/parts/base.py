@@ -18,7 +18,9 @@ Interfaces (duck-typed; the base classes below only document them and hold the d
   position        rotate_and_store(qkv, ctx, cache, heads, kv_heads)   rotate q (in place) and k, write k, v to the cache
                   project_rotate_and_store(x, w_qkv, b_qkv, ctx, cache, heads, kv_heads) -> qkv   (may fuse the three)
   block           forward(delta, res, ctx, cache) -> delta'            (arrangement of the above)
-  connection      how a sublayer reads from and writes to a stream kept in several copies (coefficients as tensors)
+  connection      how a sublayer reads from and writes to a stream kept in several copies (coefficients as tensors), a
+                  scale per channel on a sublayer's output, the weights of an average over the layers so far
+  token_input     forward(x[T, hidden], stream: LayeredStream) -> [T, hidden]   an input a layer takes from the token itself
   embedding       forward(ctx) -> res [T, hidden] float32
   head            forward(x[W, hidden]) -> logits [W, vocab] float32
 
@@ -34,7 +36,7 @@ import torch
 from ..config.model_config import PartSpec
 from ..weights.loader import TensorSpec
 
-CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "connection")
+CATEGORIES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "connection", "token_input")
 _REGISTRY: dict[str, dict[str, type]] = {c: {} for c in CATEGORIES}
 
 

@@ -8,6 +8,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 
 from ..weights.loader import TensorSpec
+from ..kernels import ops
 from .base import Part, ResidualSink, StreamValue, register_part
 
 
@@ -65,8 +66,9 @@ class Branches:
     """What a mixer may return instead of one tensor: several outputs that the block's norm adds together, each
     optionally RMS-normed over its row with ``inner_weights[k]`` first, the sum multiplied by ``coef``."""
 
-    def __init__(self, deltas, inner_weights=(), coef: float = 1.0):
+    def __init__(self, deltas, inner_weights=(), coef: float = 1.0, scaled=None):
         self.deltas, self.inner_weights, self.coef = tuple(deltas), tuple(inner_weights), coef
+        self.scaled = scaled            # (h [T, W], w float32 [T]): one more output, w[t] * h[t] (norms that add by ``add_to``)
 
 
 class PostNormResidual(Block):
@@ -163,3 +165,93 @@ class HyperConnectedMixerOnly(HyperConnected):
 
 register_part("block", "hyper_connected", HyperConnected)
 register_part("block", "hyper_connected_mixer_only", HyperConnectedMixerOnly)
+
+
+class LayerScale(Part):
+    """One learned factor per channel on a sublayer's output; the tensor is ``name`` [size]."""
+
+    def __init__(self, size: int, name: str = "scale"):
+        self.size, self.name = size, name
+
+    def tensor_specs(self):
+        return {self.name: TensorSpec((self.size,), "normal:0.5:0.2")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.vec = tensors[self.name].float().to(rt.device).contiguous()
+
+
+class DepthAverage(Part):
+    """What a layer hands on is a weighted average over depth: with X_0 the embedding and X_j the result of layer j - 1, the
+    stream after layer ``index`` becomes sum over j <= index + 1 of w[j] X_j.  The weights are the tensor ``name`` [index + 2]."""
+
+    def __init__(self, index: int, name: str = "weights"):
+        self.index, self.name = int(index), name
+
+    def tensor_specs(self):
+        n = self.index + 2
+        return {self.name: TensorSpec((n,), f"normal:{1.0 / n}:0.1")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.coef = tensors[self.name].float().to(rt.device).contiguous()
+
+
+register_part("connection", "layer_scale", LayerScale)
+register_part("connection", "depth_average", DepthAverage)
+
+
+class OutputNormResidual(Block):
+    """A layer whose norms sit on the sublayers' OUTPUTS: x <- x + scale_1 * norm_1(mixer(x)), then x <- x + scale_2 *
+    norm_2(ff(x)); both sublayers read the stream itself.  Optional parts: per-channel scales on the normed outputs
+    (``mixer_scale``, ``feed_forward_scale``), a feed-forward, an input taken from the token (``token_input``; its result is
+    RMS-normed with ``token_input_norm`` and added), and a weighted average over the results of all layers so far
+    (``depth``).  The sum, the norm and the copy of the stream for the next reader are one kernel per sublayer; the last of
+    them also stores the layer's result and takes the average.  Takes and returns a ``LayeredStream``."""
+    roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm",
+             "mixer_scale": "connection", "feed_forward_scale": "connection", "token_input": "token_input",
+             "token_input_norm": "norm", "depth": "connection"}
+    optional_roles = ("feed_forward", "feed_forward_norm", "mixer_scale", "feed_forward_scale", "token_input", "token_input_norm", "depth")
+
+    def __init__(self, **parts):
+        super().__init__(**parts)
+        for a, b in (("feed_forward", "feed_forward_norm"), ("token_input", "token_input_norm")):
+            if (a in parts) != (b in parts):
+                raise ValueError(f"a layer with a {a} needs a {b}, and the other way round")
+
+    def kernel_sources(self):
+        return {"stream_update"}
+
+    def forward(self, delta, res, ctx, cache):
+        from .embedding import LayeredStream
+        if not isinstance(delta, LayeredStream):
+            raise ValueError("a layer that norms its sublayers' outputs takes the stream from an embedding that hands on a LayeredStream")
+        s = delta
+        rt = self.mixer.rt
+        vec = lambda role: getattr(self, role).vec if hasattr(self, role) else None
+        fresh = (lambda: rt.empty(*res.shape)) if rt.dtype != res.dtype else (lambda: None)
+        x = fresh()
+        self.mixer_norm.add_to(res, self.mixer.forward(s.x, ctx, cache), vec=vec("mixer_scale"), act=x)
+        x = res if x is None else x
+        if hasattr(self, "feed_forward"):
+            nxt = fresh()
+            self.feed_forward_norm.add_to(res, self.feed_forward.forward(x, ctx), vec=vec("feed_forward_scale"), act=nxt)
+            x = res if nxt is None else nxt
+        y = norm = None
+        if hasattr(self, "token_input"):
+            y, norm = self.token_input.forward(x, s), self.token_input_norm
+        depth = getattr(self, "depth", None)
+        if y is not None or depth is not None:
+            if depth is not None and (s.history is None or depth.index + 1 >= s.history.shape[0]):
+                raise ValueError(f"the average over depth after layer {depth.index} needs a history of {depth.index + 2} entries")
+            nxt = fresh()
+            if norm is not None and getattr(self, "_input_vec", None) is None:
+                self._input_vec = norm.weight.float().contiguous()        # the kernel reads float32
+            ops.normed_add(res, (y,), vec=self._input_vec if norm is not None else None, eps=norm.eps if norm is not None else 0.0, act=nxt,
+                           history=s.history if depth is not None else None, slot=depth.index + 1 if depth is not None else 0,
+                           coef=depth.coef if depth is not None else None)
+            x = res if nxt is None else nxt
+        return LayeredStream(x, s.tokens, s.token_table, s.history)
+
+
+register_part("block", "output_norm_residual", OutputNormResidual)

@@ -6,6 +6,7 @@ from __future__ import annotations
 from ..kernels import ops
 from ..weights.loader import TensorSpec
 from .base import Part, StreamUpdated, StreamValue, register_part
+from .embedding import LayeredStream
 
 
 class RMSNorm(Part):
@@ -138,3 +139,40 @@ class DynamicTanh(Part):
 
 
 register_part("norm", "dynamic_tanh", DynamicTanh)
+
+
+class ScalarRMSNorm(Part):
+    """RMS norm whose weight is ONE number for all channels: x / sqrt(mean(x^2) + eps) * g.  Called like the other norms
+    (``norm(delta, res, rows)``) it norms the stream; ``add_to`` norms a sublayer's output and adds it to the stream (layers
+    whose norm sits on the output only)."""
+
+    def __init__(self, size: int, eps: float):
+        self.size, self.eps = size, eps
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((), "normal:1:0.1")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.gain = tensors["weight"].float().reshape(1).to(rt.device).contiguous()
+        self.weight = self.gain.expand(self.size).contiguous()         # as a vector, for the kernel that norms the stream
+
+    def kernel_sources(self):
+        return {"norm", "stream_update"}
+
+    def add_to(self, res, y, *, vec=None, act=None):
+        """res += norm(y) * vec; ``y`` a tensor or ``Branches`` (its tensors, and one scaled by a number per row, are summed)."""
+        from .block import Branches
+        if isinstance(y, Branches):
+            return ops.normed_add(res, y.deltas, scaled=y.scaled, gain=self.gain, vec=vec, eps=self.eps, act=act)
+        return ops.normed_add(res, (y,), gain=self.gain, vec=vec, eps=self.eps, act=act)
+
+    def __call__(self, delta, res, rows=None):
+        if isinstance(delta, (StreamValue, StreamUpdated, LayeredStream)):
+            delta = None
+        n_out = rows.numel() if rows is not None else res.shape[0]
+        out = self.rt.empty(n_out, self.size)
+        return ops.add_rmsnorm(delta, res, self.weight, self.eps, out, rows)
+
+
+register_part("norm", "scalar_rmsnorm", ScalarRMSNorm)
