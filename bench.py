@@ -433,10 +433,29 @@ def kebudra_configs(size: dict, vocab=32000, positions=4096):
     return kebudra, design_configs(size, vocab, positions)[1]
 
 
+def serotar_configs(size: dict, vocab=32000, positions=4096):
+    """A Serotar configuration of the given layer sizes -- latent attention without positions in every layer, a dense xIELU
+    feed-forward first and routed gated experts after it (sixteen experts and four identity experts in four groups of which
+    two are kept, four a token, and a shared expert; sized so that the matrices a token goes through equal Llama's three), a
+    hashed pair table, a per-layer token input of 256 and the average over depth -- and the Llama configuration with the same
+    width, heads and number of layers."""
+    from mini_inference_engine_b200.config import load_config
+    w, ff, H = size["width"], size["ff"], size["heads"]
+    fe = (ff // 6 + 63) // 64 * 64
+    mixer = dict(heads=H, dim=128, vdim=128, q_rank=w // 2, kv_rank=w // 4, scale=128 ** -0.5)
+    moe = dict(kind="moe", expert=dict(ff=fe), router=dict(experts=16, top=4, identity=4, groups=dict(count=4, keep=2)),
+               shared=dict(ff=ff - 4 * fe))
+    layers = [dict(type="latent_attention", mixer=mixer, mlp=dict(kind="dense", ff=ff) if i == 0 else moe) for i in range(size["layers"])]
+    serotar = load_config(dict(architecture="Serotar", vocab=vocab, width=w, norm=dict(eps=1e-5), token_side=dict(dim=256),
+                               embedding=dict(scale=w ** 0.5, bigram=dict(buckets=65521, mul_prev=31337, mul_cur=257)), layers=layers))
+    return serotar, design_configs(size, vocab, positions)[1]
+
+
 KERNEL_FACES = ("embedding", "add_rmsnorm", "stream_norm", "rope_cache_write", "qk_norm_rope", "paged_attention", "prefill_attention",
                 "prefill_attention_tc", "decode_attention", "retention_scan", "head_rms_gate", "causal_conv", "recurrence_gates",
                 "recurrence_scan", "swiglu", "glu_clamped", "sigmoid_gate", "hyper_norm", "latent_norm_rope", "latent_assemble",
-                "diff_combine", "delta_prepare", "conv_state_update", "delta_scan", "head_norm_gate", "moe_route", "moe_router", "moe_dense_act", "moe_pairs", "moe_sort", "moe_gather", "moe_act_rows", "moe_combine", "grouped_linear")
+                "diff_combine", "delta_prepare", "conv_state_update", "delta_scan", "head_norm_gate", "moe_route", "moe_router", "moe_dense_act", "moe_pairs", "moe_sort", "moe_gather", "moe_act_rows", "moe_combine", "grouped_linear",
+                "pair_embedding", "normed_add", "xielu", "gelu_gate_rows", "moe_glu")
 
 
 class KernelTimes:
@@ -491,7 +510,7 @@ def run_design(args, steps, warmup):
     from mini_inference_engine_b200 import EngineConfig, LLMEngine
     from mini_inference_engine_b200.weights import write_model_folder
     pk = peaks()
-    configs_for = {"getizen": design_configs, "kebudra": kebudra_configs}[args.design]
+    configs_for = {"getizen": design_configs, "kebudra": kebudra_configs, "serotar": serotar_configs}[args.design]
     out = {"metric": "design_comparison", "design": args.design.capitalize(), "beside": "Llama", "dtype": "bf16", "data": "synthetic (random weights, seed 0)",
            "peaks": pk, "sizes": {}}
     batches = [int(b) for b in args.points.split(",") if b] or [8]
@@ -557,7 +576,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--preset", default="tinyllama-1.1b")
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
-    ap.add_argument("--design", default=None, choices=["getizen", "kebudra"],
+    ap.add_argument("--design", default=None, choices=["getizen", "kebudra", "serotar"],
                     help="instead of the default workload: prefill and decode throughput of this design beside Llama at equal "
                          "layer sizes (--sizes), random weights; decode batches from --points")
     ap.add_argument("--sizes", default="w2048,w4096", help="with --design: layer sizes to measure, of " + ", ".join(DESIGN_SIZES))
