@@ -43,14 +43,25 @@ typedef __nv_bfloat16 bf16;
 struct GpParams {
     void* out;               // [M, N] (or [M, N / 2] with SwiGLU), bfloat16 or float32
     const void* bias;        // [N] or null
-    int bias_tag, out_f32, swiglu;
+    int bias_tag, out_f32, swiglu;           // swiglu 1: the gated epilogue; 2: an activation on every output (xIELU), y stays N wide
     float glu_limit, glu_slope, glu_shift;   // the gated epilogue's shape: g' sigmoid(slope g') (u' + shift) with clamps at +-limit (<= 0: none); 0, 1, 0 is SwiGLU
+                                             // with swiglu 2: slope = a_p, shift = a_n of a_p z^2 + z / 2 (z > 0), a_n (exp(z) - 1 - z) + z / 2 (z <= 0)
     int M, N, K;
     int tiles_m, num_tiles, k_tiles, stages;
     int* error;
     float* res; const void* norm_w; int norm_w_tag; bf16* xw_out; float* sq_out; int sq_stride;
     const float* sq_in; int sq_slots, sq_in_stride; float sq_width, sq_eps;
 };
+
+// xIELU on a float32 sum, cheap enough to hide behind the next tile's MMAs (256 values a thread and tile): the exponential
+// arm's exp(z) - 1 - z by the fast exponential, and by its series z^2 (1/2 + z/6 + z^2/24) near 0, where the difference
+// would cancel (next term z^5 / 120: below 2e-5 of the value for z > -0.1).  The result is rounded to bfloat16.
+__device__ __forceinline__ float xielu_epilogue(float z, float ap, float an) {
+    const float half = 0.5f * z;
+    const float series = z * z * fmaf(z, fmaf(z, 1.f / 24.f, 1.f / 6.f), 0.5f);
+    const float arm = z > -0.1f ? series : __expf(z) - 1.f - z;
+    return z > 0.f ? fmaf(ap * z, z, half) : fmaf(an, arm, half);
+}
 
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
     asm volatile(
@@ -237,7 +248,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     }
                     continue;
                 }
-                if (p.swiglu) {
+                if (p.swiglu == 2) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = xielu_epilogue(v[i], p.glu_slope, p.glu_shift);
+                    }
+                }
+                if (p.swiglu == 1) {
                     // interleaved rows of w: column 2i the gate, 2i + 1 the value
                     float o[16];
 #pragma unroll
@@ -332,7 +349,7 @@ extern "C" int mie_gemm_pair(const void* x, const void* w, const void* bias, int
                              int K, int swiglu, float glu_limit, float glu_slope, float glu_shift, const GpFuse* fuse,
                              cudaStream_t stream) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
-    if (K % 8 || N % 8 || (swiglu && N % 16)) return MIE_ERR_BAD_ARG;
+    if (K % 8 || N % 8 || (swiglu == 1 && N % 16) || swiglu < 0 || swiglu > 2) return MIE_ERR_BAD_ARG;
     const bool into_stream = fuse && fuse->res;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | (into_stream ? 0 : reinterpret_cast<uintptr_t>(y))) & 15) return MIE_ERR_BAD_ARG;
     if (!into_stream && (!y || (y_tag != MIE_BF16 && y_tag != MIE_F32))) return MIE_ERR_BAD_ARG;
@@ -348,7 +365,7 @@ extern "C" int mie_gemm_pair(const void* x, const void* w, const void* bias, int
     if ((rc = make_map_rows(&mx, x, M, K))) return rc;
     if ((rc = make_map_rows(&mw, w, N, K))) return rc;
     GpParams p;
-    p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.out_f32 = y_tag == MIE_F32; p.swiglu = swiglu ? 1 : 0;
+    p.out = y; p.bias = bias; p.bias_tag = bias_tag; p.out_f32 = y_tag == MIE_F32; p.swiglu = swiglu;
     p.glu_limit = glu_limit; p.glu_slope = glu_slope; p.glu_shift = glu_shift;
     p.M = M; p.N = N; p.K = K;
     p.tiles_m = (M + 2 * GP_BM - 1) / (2 * GP_BM);

@@ -136,35 +136,61 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int* __restrict__ 
 }
 
 #define ROUTER_TOKENS 8      // tokens a block: the router's matrix is read once for all of them
+#define ROUTER_THREADS 512
 
-// A block per ROUTER_TOKENS tokens: their inputs into shared memory as float32, a warp per expert in turn for the logits of
-// all of them (the expert's row is read once), then a thread per token chooses.  `logits` (optional) receives z.
+// Column segments a row's dot product is cut into, so that a block's warps all have work when there are few outputs: a
+// function of the sizes only (never of the batch), so a token's logits are summed in one order whatever runs beside it.
+static __host__ __device__ inline int router_segments(int E, int h, int warps) {
+    int S = 1;
+    while (S < 8 && E * S < 4 * warps && (h + 2 * S - 1) / (2 * S) >= 128) S <<= 1;
+    return S;
+}
+
+// A block per ROUTER_TOKENS tokens: their inputs into shared memory as float32, a warp per (output, column segment) in turn
+// for the logits of all of them (the output's row is read once a block), the segments' sums added in their order, then a
+// warp per token for the scores and a thread per token chooses.  `logits` (optional) receives z.
 template <typename TA>
-__global__ void moe_router_kernel(const TA* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
-                                  float* __restrict__ logits, int num_tokens, int h, int E, int top, int tpb, RouteRule rr) {
-    extern __shared__ __align__(16) float rs[];               // x [tpb, h], then z [tpb, E]
+__global__ void __launch_bounds__(ROUTER_THREADS)
+moe_router_kernel(const TA* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
+                  float* __restrict__ logits, int num_tokens, int h, int E, int top, int tpb, int S, RouteRule rr) {
+    extern __shared__ __align__(16) float rs[];               // x [tpb, h], then z [tpb, E], then the segments' sums [S, tpb, E]
     float* z = rs + (size_t)tpb * h;
+    float* zp = z + (size_t)tpb * E;
     pdl_enter();
     const int t0 = blockIdx.x * tpb, nt = min(tpb, num_tokens - t0);
-    for (int c = threadIdx.x; c < nt * h; c += blockDim.x) rs[c] = to_f32<TA>(x[(int64_t)t0 * h + c]);
+    const TA* xb = x + (int64_t)t0 * h;
+    if (sizeof(TA) == 2 && (h & 7) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {      // eight inputs a load
+        for (int c = threadIdx.x * 8; c < nt * h; c += blockDim.x * 8) {
+            const uint4 u = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(xb) + c);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+            const float2 a = __bfloat1622float2(p[0]), b = __bfloat1622float2(p[1]), c2 = __bfloat1622float2(p[2]), d = __bfloat1622float2(p[3]);
+            *reinterpret_cast<float4*>(rs + c) = make_float4(a.x, a.y, b.x, b.y);
+            *reinterpret_cast<float4*>(rs + c + 4) = make_float4(c2.x, c2.y, d.x, d.y);
+        }
+    } else {
+        for (int c = threadIdx.x; c < nt * h; c += blockDim.x) rs[c] = to_f32<TA>(xb[c]);
+    }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const bool vec = (h & 3) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
-    for (int e = warp; e < E; e += nw) {
+    const int seg = ((h + S - 1) / S + 127) / 128 * 128;      // columns a segment, whole 128-column steps
+    for (int item = warp; item < E * S; item += nw) {
+        const int e = item / S, s = item - e * S;
+        const int c_begin = s * seg, c_end = min(h, c_begin + seg);
         const float* row = w + (int64_t)e * h;
         float acc[ROUTER_TOKENS];
 #pragma unroll
         for (int i = 0; i < ROUTER_TOKENS; ++i) acc[i] = 0.f;
         if (vec) {
-            for (int c0 = lane * 4; c0 < h; c0 += 512) {           // four 16-byte loads of the row in flight
+            for (int c0 = c_begin + lane * 4; c0 < c_end; c0 += 512) {           // four 16-byte loads of the row in flight
                 float4 a[4];
 #pragma unroll
                 for (int u = 0; u < 4; ++u)
-                    a[u] = c0 + 128 * u < h ? *reinterpret_cast<const float4*>(row + c0 + 128 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    a[u] = c0 + 128 * u < c_end ? *reinterpret_cast<const float4*>(row + c0 + 128 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int c = c0 + 128 * u;
-                    if (c >= h) break;
+                    if (c >= c_end) break;
 #pragma unroll
                     for (int i = 0; i < ROUTER_TOKENS; ++i)
                         if (i < nt) {
@@ -175,7 +201,7 @@ __global__ void moe_router_kernel(const TA* __restrict__ x, const float* __restr
                 }
             }
         } else {
-            for (int c = lane; c < h; c += 32) {
+            for (int c = c_begin + lane; c < c_end; c += 32) {
                 const float a = row[c];
 #pragma unroll
                 for (int i = 0; i < ROUTER_TOKENS; ++i)
@@ -185,8 +211,14 @@ __global__ void moe_router_kernel(const TA* __restrict__ x, const float* __restr
 #pragma unroll
         for (int i = 0; i < ROUTER_TOKENS; ++i) {
             const float v = warp_sum(acc[i]);
-            if (lane == 0 && i < nt) z[i * E + e] = v;
+            if (lane == 0 && i < nt) zp[((size_t)s * tpb + i) * E + e] = v;
         }
+    }
+    __syncthreads();
+    for (int c = threadIdx.x; c < nt * E; c += blockDim.x) {
+        float v = zp[c];
+        for (int s = 1; s < S; ++s) v += zp[(size_t)s * tpb * E + c];
+        z[c] = v;
     }
     __syncthreads();
     if (logits)
@@ -244,20 +276,26 @@ template <> __device__ __forceinline__ void load8<float>(const float* p, float* 
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-// The dot product of a matrix row (n entries, 16-byte aligned, n a multiple of 8) with a float32 vector in shared memory.
-template <typename TW>
-__device__ __forceinline__ float row_dot(const TW* __restrict__ row, const float* __restrict__ x, int n, int lane) {
-    float acc = 0.f;
-    for (int c = lane * 8; c < n; c += 256) {
-        float w[8];
-        load8<TW>(row + c, w);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc = fmaf(w[i], x[c + i], acc);
-    }
-    return warp_sum(acc);
-}
-
 #define MOE_ROWS_PER_WARP 4
+
+// The dot products of MOE_ROWS_PER_WARP matrix rows (`stride` entries apart, the last ones repeated past `rows`) with one float32
+// vector in shared memory, added to acc[]: every row's 16-byte load of a step is issued before any is used, so a warp keeps
+// that many loads in flight.  acc[] holds the lane's partial sums; the caller adds the lanes up once a row.
+template <typename TW>
+__device__ __forceinline__ void rows_dot(const TW* __restrict__ first, int64_t stride, int rows, const float* __restrict__ x, int n,
+                                         int lane, float* acc) {
+    for (int c = lane * 8; c < n; c += 256) {
+        float w[MOE_ROWS_PER_WARP][8];
+#pragma unroll
+        for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) load8<TW>(first + (int64_t)min(r, rows - 1) * stride + c, w[r]);
+        const float4 xa = *reinterpret_cast<const float4*>(x + c), xb = *reinterpret_cast<const float4*>(x + c + 4);
+        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+        for (int r = 0; r < MOE_ROWS_PER_WARP; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[r] = fmaf(w[r][i], xv[i], acc[r]);
+    }
+}
 
 template <typename TA, typename TW>
 __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restrict__ w_up, const int* __restrict__ ids,
@@ -272,16 +310,19 @@ __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restri
     for (int c = threadIdx.x; c < h; c += blockDim.x) xs[c] = to_f32<TA>(x[(int64_t)t * h + c]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int f0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP;
-    for (int f = f0; f < min(f0 + MOE_ROWS_PER_WARP, F); ++f) {
-        float v;
-        if (gated) {
-            const float g = row_dot<TW>(w_up + ((int64_t)e * 2 * F + f) * h, xs, h, lane);
-            v = expert_act(g, kind) * row_dot<TW>(w_up + ((int64_t)e * 2 * F + F + f) * h, xs, h, lane);
-        } else {
-            v = expert_act(row_dot<TW>(w_up + ((int64_t)e * F + f) * h, xs, h, lane), kind);
-        }
-        if (lane == 0) hid[(int64_t)pair * F + f] = from_f32<TA>(weight * v);
+    const int f0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP, rows = min(MOE_ROWS_PER_WARP, F - f0);
+    if (rows <= 0) return;
+    float g[MOE_ROWS_PER_WARP], u[MOE_ROWS_PER_WARP];
+#pragma unroll
+    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) g[r] = u[r] = 0.f;
+    const TW* base = w_up + ((int64_t)e * (gated ? 2 : 1) * F + f0) * h;
+    rows_dot<TW>(base, h, rows, xs, h, lane, g);
+    if (gated) rows_dot<TW>(base + (int64_t)F * h, h, rows, xs, h, lane, u);
+#pragma unroll
+    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) {
+        const float gs = warp_sum(g[r]);
+        const float v = gated ? expert_act(gs, kind) * warp_sum(u[r]) : expert_act(gs, kind);
+        if (lane == 0 && r < rows) hid[(int64_t)pair * F + f0 + r] = from_f32<TA>(weight * v);
     }
 }
 
@@ -295,21 +336,27 @@ __global__ void moe_pairs_down_kernel(const TA* __restrict__ hid, const TW* __re
         hs[c] = ids[t * top + c / F] < E ? to_f32<TA>(hid[(int64_t)t * top * F + c]) : 0.f;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int n0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP;
-    for (int n = n0; n < min(n0 + MOE_ROWS_PER_WARP, h); ++n) {
-        float acc = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int e = ids[t * top + k];
-            if (e < E) acc += row_dot<TW>(w_down + (int64_t)n * E * F + (int64_t)e * F, hs + k * F, F, lane);
-        }
-        if (lane == 0) out[(int64_t)t * h + n] = acc;
+    const int n0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP, rows = min(MOE_ROWS_PER_WARP, h - n0);
+    if (rows <= 0) return;
+    float acc[MOE_ROWS_PER_WARP];
+#pragma unroll
+    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) acc[r] = 0.f;
+    for (int k = 0; k < top; ++k) {                           // a lane's sums run over the choices in their order, then the lanes are added
+        const int e = ids[t * top + k];
+        if (e < E) rows_dot<TW>(w_down + (int64_t)n0 * E * F + (int64_t)e * F, (int64_t)E * F, rows, hs + k * F, F, lane, acc);
+    }
+#pragma unroll
+    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) {
+        const float v = warp_sum(acc[r]);
+        if (lane == 0 && r < rows) out[(int64_t)t * h + n0 + r] = v;
     }
 }
 
 template <typename TA, typename TW>
 static int launch_pairs(const void* x, const void* w_up, const void* w_down, const int* ids, const float* wts, void* hid, float* out,
                         int T, int h, int E, int F, int top, int kind, int gated, cudaStream_t stream) {
-    const int threads = 256, rows = (threads / 32) * MOE_ROWS_PER_WARP;
+    // fewer warps a block where a handful of tokens would leave SMs without one (the warps' work does not depend on it)
+    const int threads = (int64_t)T * ((h + 31) / 32) < 2 * device_sm_count() ? 128 : 256, rows = (threads / 32) * MOE_ROWS_PER_WARP;
     const size_t smem_up = (size_t)h * sizeof(float), smem_down = (size_t)top * F * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(moe_pairs_up_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
     if (e != cudaSuccess) return (int)e;
@@ -422,6 +469,33 @@ __global__ void moe_combine_kernel(const T* __restrict__ rows, const int* __rest
     }
 }
 
+// The same, eight bfloat16 a thread (16-byte loads, two 16-byte stores); h8 = h / 8.
+__global__ void moe_combine_bf16x8_kernel(const bf16* __restrict__ rows, const int* __restrict__ place, float* __restrict__ out,
+                                          int num_tokens, int h8, int top, const int* __restrict__ ids, int real) {
+    pdl_enter();
+    const int64_t total = (int64_t)num_tokens * h8;
+    for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / h8), c = (int)(idx - (int64_t)t * h8);
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+        for (int k = 0; k < top; ++k) {
+            if (ids && ids[t * top + k] >= real) continue;
+            const uint4 u = *reinterpret_cast<const uint4*>(rows + ((int64_t)place[t * top + k] * h8 + c) * 8);
+            const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p[i]);
+                acc[2 * i] += f.x;
+                acc[2 * i + 1] += f.y;
+            }
+        }
+        float4* o = reinterpret_cast<float4*>(out + idx * 8);
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+}
+
 static int capped_blocks(int64_t items, int threads) {
     int64_t blocks = (items + threads - 1) / threads;
     if (blocks > (int64_t)device_sm_count() * 16) blocks = (int64_t)device_sm_count() * 16;
@@ -471,6 +545,9 @@ extern "C" int mie_moe_combine(const void* rows, const int* place, float* out, i
     if (num_tokens <= 0) return 0;
     if (h <= 0 || top <= 0) return MIE_ERR_BAD_ARG;
     const int64_t items = (int64_t)num_tokens * h;
+    if (tag == MIE_BF16 && h % 8 == 0 && ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(out)) & 15) == 0)
+        return launch_kernel(moe_combine_bf16x8_kernel, dim3(capped_blocks(items / 8, 256)), dim3(256), 0, stream, (const bf16*)rows, place,
+                             out, num_tokens, h / 8, top, ids, real);
     if (tag == MIE_F32)
         return launch_kernel(moe_combine_kernel<float>, dim3(capped_blocks(items, 256)), dim3(256), 0, stream, (const float*)rows, place, out,
                              num_tokens, h, top, ids, real);
@@ -496,19 +573,21 @@ extern "C" int mie_moe_router(const void* x, int tag, const float* w, int* ids, 
     if (E <= 0 || top <= 0 || top > E || h <= 0) return MIE_ERR_BAD_ARG;
     const RouteRule rr{mode, correction, groups, keep, real, rest};
     if (!rule_ok(rr, E, top)) return MIE_ERR_BAD_ARG;
+    const int threads = ROUTER_THREADS;
+    const int S = router_segments(E, h, threads / 32);
     int tpb = ROUTER_TOKENS;                                   // fewer where the tokens' inputs would not fit in 96 KB ...
-    while (tpb > 1 && (size_t)tpb * (h + E) * sizeof(float) > 96 * 1024) tpb >>= 1;
+    while (tpb > 1 && (size_t)tpb * (h + (S + 1) * E) * sizeof(float) > 96 * 1024) tpb >>= 1;
     while (tpb > 1 && (num_tokens + tpb - 1) / tpb < device_sm_count()) tpb >>= 1;      // ... or would leave SMs without a block
-    const size_t smem = (size_t)tpb * (h + E) * sizeof(float);
+    const size_t smem = (size_t)tpb * (h + (S + 1) * E) * sizeof(float);
     if (smem > 200 * 1024) return MIE_ERR_TOO_LARGE;
-    const int threads = 256, blocks = (num_tokens + tpb - 1) / tpb;
+    const int blocks = (num_tokens + tpb - 1) / tpb;
     cudaError_t e;
     if (tag == MIE_F32) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_kernel(moe_router_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb, rr);
+        return launch_kernel(moe_router_kernel<float>, dim3(blocks), dim3(threads), smem, stream, (const float*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb, S, rr);
     } else if (tag == MIE_BF16) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
-        return launch_kernel(moe_router_kernel<bf16>, dim3(blocks), dim3(threads), smem, stream, (const bf16*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb, rr);
+        return launch_kernel(moe_router_kernel<bf16>, dim3(blocks), dim3(threads), smem, stream, (const bf16*)x, w, ids, wts, logits, num_tokens, h, E, top, tpb, S, rr);
     }
     return MIE_ERR_BAD_ARG;
 }

@@ -388,14 +388,20 @@ def pair_supports(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, swiglu: b
 
 
 def gemm_pair(x, w: torch.Tensor, out: torch.Tensor | None, bias: torch.Tensor | None = None, swiglu: bool = False,
-              res: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0, glu=None):
+              res: torch.Tensor | None = None, norm_weight: torch.Tensor | None = None, eps: float = 0.0, glu=None, xielu=None):
     """out = x w^T (+ bias), or silu(gate) * value over interleaved rows of ``w`` with ``swiglu``: the product
     for many tokens on pairs of SMs (``csrc/gemm_pair_tc.cu``: 256 x 256 tiles by cta_group::2 MMAs, two
     accumulators in tensor memory, one persistent pair of blocks per two SMs).  ``x`` may be a DeferredNorm (the
     norm in front becomes a row factor on the sums).  With ``res`` (float32 [M, N]) the product is added to it
     in place instead of being written (``out`` is None); with ``norm_weight`` as well, the DeferredNorm for the
-    product behind that norm is returned."""
+    product behind that norm is returned.  ``xielu`` = (a_p, a_n): every output goes through that activation in the
+    epilogue (a_p z^2 + z / 2 for z > 0, a_n (exp(z) - 1 - z) + z / 2 else), in float32 before it is rounded."""
     glu = tuple(float(v) for v in (glu or SWIGLU))        # the gated epilogue's shape, as for ``gemm``
+    mode = int(swiglu)
+    if xielu is not None:
+        if swiglu or res is not None:
+            raise GemmTcError("gemm_pair: the activation epilogue goes with a plain product")
+        mode, glu = 2, (0.0, float(xielu[0]), float(xielu[1]))
     deferred = x if isinstance(x, DeferredNorm) else None
     xt = deferred.xw if deferred is not None else x
     M, K = xt.shape
@@ -418,7 +424,7 @@ def gemm_pair(x, w: torch.Tensor, out: torch.Tensor | None, bias: torch.Tensor |
         raise GemmTcError(f"gemm_pair: out {None if out is None else tuple(out.shape)} for a product of {(M, N)}")
     fuse = _fuse_struct(deferred, res, norm_weight, xw, sq)
     ops._check(lib.mie_gemm_pair(ops._ptr(xt), ops._ptr(w), ops._ptr(bias), ops.tag(bias) if bias is not None else 0,
-                                 ops._ptr(out), ops.tag(out) if out is not None else 0, M, N, K, int(swiglu),
+                                 ops._ptr(out), ops.tag(out) if out is not None else 0, M, N, K, mode,
                                  ctypes.c_float(glu[0]), ctypes.c_float(glu[1]), ctypes.c_float(glu[2]),
                                  ctypes.byref(fuse), ops._stream()), "gemm_pair")
     return made if res is not None else out

@@ -137,6 +137,19 @@ def linear(x, w: torch.Tensor, bias, out_dtype: torch.dtype) -> torch.Tensor:
     return out
 
 
+def linear_xielu(x: torch.Tensor, w: torch.Tensor, ap: float, an: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """xielu(x W^T) with the constants a_p, a_n: fused into the epilogue of the product on pairs of SMs where that kernel runs
+    (prompt-sized steps in bfloat16), else the product followed by the activation kernel."""
+    M = x.shape[0]
+    if (M and takes_pair(M, w) and x.dtype == torch.bfloat16 and out_dtype in (torch.bfloat16, torch.float32) and x.is_contiguous()
+            and not isinstance(x, gemm_tc.DeferredNorm)):
+        out = torch.empty(M, w.shape[0], dtype=out_dtype, device=w.device)
+        if gemm_tc.pair_supports(x, w, out):
+            return gemm_tc.gemm_pair(x, w, out, xielu=(ap, an))
+    up = linear(x, w, None, out_dtype)
+    return ops.xielu(up, torch.empty_like(up), ap, an)
+
+
 def linear_swiglu(x: torch.Tensor, w_interleaved: torch.Tensor, out_dtype: torch.dtype, glu=None) -> torch.Tensor:
     """silu(x Wg^T) * (x Wu^T) for a weight whose rows alternate gate_i, up_i: fused into the
     tcgen05 product's epilogue where that kernel runs, else the product followed by the SwiGLU kernel.

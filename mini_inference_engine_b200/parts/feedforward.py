@@ -130,8 +130,8 @@ class ActivatedMLP(FeedForward):
         return {"activation"} | self.rt.product_sources(self.w_up, self.w_down)
 
     def forward(self, x, ctx):
-        up = self.rt.linear(x, self.w_up)
-        return self.rt.linear(ops.xielu(up, torch.empty_like(up), self.ap, self.an), self.w_down, None, out_dtype=torch.float32)
+        act = linear_kernels.linear_xielu(x, self.w_up, self.ap, self.an, self.rt.dtype)      # the activation in the product's epilogue
+        return self.rt.linear(act, self.w_down, None, out_dtype=torch.float32)
 
 
 register_part("feed_forward", "activated_mlp", ActivatedMLP)

@@ -224,7 +224,69 @@ def test_token_input_gated_by_the_stream(dt, hid, dim, index):
     close(got, want, dt)
 
 
+def test_xielu_in_the_epilogue_of_the_prompt_sized_product():
+    """From 128 tokens on the up product of a bfloat16 model runs on pairs of SMs and applies the activation to its float32
+    sums; the plain implementation applies it to the unrounded product too."""
+    from mini_inference_engine_b200.kernels import linear as lk
+    g = torch.Generator().manual_seed(11)
+    ran = 0
+    for T, hid, ff, p, q in ((2048, 128, 1792, 0.4, -0.6), (3000, 64, 3072, -1.0, 1.5), (4100, 72, 4600 // 8 * 8, 0.0, 0.0)):
+        x = (torch.randn(T, hid, generator=g)).bfloat16()
+        w = (torch.randn(ff, hid, generator=g) * hid ** -0.5 * 3).bfloat16()
+        ap, an = math.log1p(math.exp(p)), 0.5 + math.log1p(math.exp(q))
+        if not lk.takes_pair(T, w.to(DEV)):          # sizes that fill too few of this device's pairs of SMs
+            continue
+        ran += 1
+        got = lk.linear_xielu(x.to(DEV), w.to(DEV), ap, an, torch.bfloat16)
+        want = ps.xielu(x.float() @ w.float().t(), torch.tensor([p, q]))
+        close(got, want, torch.bfloat16, f"{T} tokens", bf16=1e-2)
+        # and the product followed by the activation kernel, which small steps use, agrees up to the rounding between them
+        up = lk.linear(x[:8].to(DEV), w.to(DEV), None, torch.bfloat16)
+        from mini_inference_engine_b200.kernels import ops
+        close(ops.xielu(up, torch.empty_like(up), ap, an), want[:8], torch.bfloat16, "8 tokens", bf16=2e-2)
+    if not ran:
+        pytest.skip("the paired product takes none of these sizes on this device")
+
+
 # ----------------------------------------------------------------------------------------------- router and experts
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("width,outputs", [(1024, 5), (1000, 20), (2050, 3), (4096, 8), (512, 40), (333, 2)])
+def test_router_logits_of_wide_inputs_do_not_depend_on_the_batch(dt, width, outputs):
+    """Wide inputs with few outputs: a row's dot product is cut into column segments (16-byte and scalar paths); a token's
+    logits are the same numbers whatever else is in the batch."""
+    from mini_inference_engine_b200.kernels import ops
+    g = torch.Generator().manual_seed(width + outputs)
+    x = torch.randn(700, width, generator=g).to(dt)
+    wr = torch.randn(outputs, width, generator=g) * width ** -0.5
+    top = min(2, outputs)
+    whole = torch.empty(700, outputs, device=DEV)
+    ids, wts = ops.moe_router(x.to(DEV), wr.to(DEV), top, whole)
+    want = x.double() @ wr.double().t()
+    assert torch.allclose(whole.cpu().double(), want, atol=2e-5, rtol=1e-5)
+    order = want.topk(top, -1).indices
+    sure = (want.topk(top + 1, -1).values.diff(dim=-1).abs().min(-1).values > 1e-4) if outputs > top else torch.ones(700, dtype=torch.bool)
+    assert torch.equal(ids.cpu().long()[sure], order[sure])
+    for rows in ([0], [5, 6, 7], list(range(100, 109)), list(range(400, 700))):
+        part = torch.empty(len(rows), outputs, device=DEV)
+        ops.moe_router(x[rows].contiguous().to(DEV), wr.to(DEV), top, part)
+        assert torch.equal(part, whole[rows]), f"rows {rows[:3]}.. of width {width}"
+
+
+def test_expert_rows_are_summed_per_token_in_order():
+    from mini_inference_engine_b200.kernels import ops
+    g = torch.Generator().manual_seed(3)
+    for T, top, h, real in ((37, 3, 64, 5), (300, 4, 1024, 6), (9, 2, 50, 4)):
+        ids = torch.stack([torch.randperm(8, generator=g)[:top] for _ in range(T)]).int()
+        place = torch.randperm(T * top, generator=g).int()
+        for dt in DTYPES:
+            rows = torch.randn(T * top, h, generator=g).to(dt)
+            want = torch.zeros(T, h)
+            for k in range(top):
+                want += rows.float()[place.view(T, top)[:, k].long()] * (ids[:, k:k + 1] < real)
+            got = ops.moe_combine(rows.to(DEV), place.to(DEV), top, torch.empty(T, h, device=DEV), ids.to(DEV), real)
+            assert torch.allclose(got.cpu(), want, atol=1e-5), (T, top, h, dt)
+
 
 def test_router_scores_all_outputs_and_chooses_within_the_best_groups():
     from mini_inference_engine_b200.kernels import ops
