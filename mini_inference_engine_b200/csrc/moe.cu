@@ -276,28 +276,48 @@ template <> __device__ __forceinline__ void load8<float>(const float* p, float* 
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-#define MOE_ROWS_PER_WARP 4
-
-// The dot products of MOE_ROWS_PER_WARP matrix rows (`stride` entries apart, the last ones repeated past `rows`) with one float32
-// vector in shared memory, added to acc[]: every row's 16-byte load of a step is issued before any is used, so a warp keeps
-// that many loads in flight.  acc[] holds the lane's partial sums; the caller adds the lanes up once a row.
-template <typename TW>
-__device__ __forceinline__ void rows_dot(const TW* __restrict__ first, int64_t stride, int rows, const float* __restrict__ x, int n,
-                                         int lane, float* acc) {
-    for (int c = lane * 8; c < n; c += 256) {
-        float w[MOE_ROWS_PER_WARP][8];
+// The dot products of R matrix rows (`stride` entries apart, the last ones repeated past `rows`) of each of M matrices (`gap`
+// entries apart) with one float32 vector in shared memory, added to acc[m * R + r]: U column steps of 256 entries are taken at a
+// time, and all R * U * M 16-byte loads of a lane are issued before any is used, so a warp keeps that many in flight.  acc[] holds
+// the lane's partial sums (a row's columns in their order); the caller adds the lanes up once a row.
+template <typename TW, int R, int U, int M>
+__device__ __forceinline__ void rows_dot(const TW* __restrict__ first, int64_t gap, int64_t stride, int rows, const float* __restrict__ x,
+                                         int n, int lane, float* acc) {
+    for (int c0 = lane * 8; c0 < n; c0 += 256 * U) {
+        float w[M][R][U][8];
 #pragma unroll
-        for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) load8<TW>(first + (int64_t)min(r, rows - 1) * stride + c, w[r]);
-        const float4 xa = *reinterpret_cast<const float4*>(x + c), xb = *reinterpret_cast<const float4*>(x + c + 4);
-        const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+        for (int m = 0; m < M; ++m)
 #pragma unroll
-        for (int r = 0; r < MOE_ROWS_PER_WARP; ++r)
+            for (int r = 0; r < R; ++r)
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[r] = fmaf(w[r][i], xv[i], acc[r]);
+                for (int u = 0; u < U; ++u) {
+                    const int c = c0 + 256 * u;
+                    if (c < n) load8<TW>(first + m * gap + (int64_t)min(r, rows - 1) * stride + c, w[m][r][u]);
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) w[m][r][u][i] = 0.f;
+                    }
+                }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int c = c0 + 256 * u;
+            if (c >= n) break;
+            const float4 xa = *reinterpret_cast<const float4*>(x + c), xb = *reinterpret_cast<const float4*>(x + c + 4);
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+            for (int m = 0; m < M; ++m)
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[m * R + r] = fmaf(w[m][r][u][i], xv[i], acc[m * R + r]);
+        }
     }
 }
 
-template <typename TA, typename TW>
+// R rows a warp and U column steps at a time: (4, 1) where the batch gives every SM its fill of warps, (1, 4) for a handful of
+// tokens, where more and narrower warps keep as many bytes in flight.  A row's sum runs over its columns in the same order
+// either way, so the result does not depend on the choice.
+template <typename TA, typename TW, int R, int U>
 __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restrict__ w_up, const int* __restrict__ ids,
                                     const float* __restrict__ wts, TA* __restrict__ hid, int h, int E, int F, int top, int kind,
                                     int gated) {
@@ -310,23 +330,23 @@ __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restri
     for (int c = threadIdx.x; c < h; c += blockDim.x) xs[c] = to_f32<TA>(x[(int64_t)t * h + c]);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int f0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP, rows = min(MOE_ROWS_PER_WARP, F - f0);
+    const int f0 = (blockIdx.y * nw + warp) * R, rows = min(R, F - f0);
     if (rows <= 0) return;
-    float g[MOE_ROWS_PER_WARP], u[MOE_ROWS_PER_WARP];
+    float gu[2 * R];                                           // gate sums, then up sums
 #pragma unroll
-    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) g[r] = u[r] = 0.f;
+    for (int r = 0; r < 2 * R; ++r) gu[r] = 0.f;
     const TW* base = w_up + ((int64_t)e * (gated ? 2 : 1) * F + f0) * h;
-    rows_dot<TW>(base, h, rows, xs, h, lane, g);
-    if (gated) rows_dot<TW>(base + (int64_t)F * h, h, rows, xs, h, lane, u);
+    if (gated) rows_dot<TW, R, U, 2>(base, (int64_t)F * h, h, rows, xs, h, lane, gu);
+    else rows_dot<TW, R, U, 1>(base, 0, h, rows, xs, h, lane, gu);
 #pragma unroll
-    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) {
-        const float gs = warp_sum(g[r]);
-        const float v = gated ? expert_act(gs, kind) * warp_sum(u[r]) : expert_act(gs, kind);
+    for (int r = 0; r < R; ++r) {
+        const float gs = warp_sum(gu[r]);
+        const float v = gated ? expert_act(gs, kind) * warp_sum(gu[R + r]) : expert_act(gs, kind);
         if (lane == 0 && r < rows) hid[(int64_t)pair * F + f0 + r] = from_f32<TA>(weight * v);
     }
 }
 
-template <typename TA, typename TW>
+template <typename TA, typename TW, int R, int U>
 __global__ void moe_pairs_down_kernel(const TA* __restrict__ hid, const TW* __restrict__ w_down, const int* __restrict__ ids,
                                       float* __restrict__ out, int h, int E, int F, int top) {
     extern __shared__ __align__(16) float hs[];               // the token's `top` hidden rows, float32 [top, F]
@@ -336,37 +356,49 @@ __global__ void moe_pairs_down_kernel(const TA* __restrict__ hid, const TW* __re
         hs[c] = ids[t * top + c / F] < E ? to_f32<TA>(hid[(int64_t)t * top * F + c]) : 0.f;
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    const int n0 = (blockIdx.y * nw + warp) * MOE_ROWS_PER_WARP, rows = min(MOE_ROWS_PER_WARP, h - n0);
+    const int n0 = (blockIdx.y * nw + warp) * R, rows = min(R, h - n0);
     if (rows <= 0) return;
-    float acc[MOE_ROWS_PER_WARP];
+    float acc[R];
 #pragma unroll
-    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) acc[r] = 0.f;
+    for (int r = 0; r < R; ++r) acc[r] = 0.f;
     for (int k = 0; k < top; ++k) {                           // a lane's sums run over the choices in their order, then the lanes are added
         const int e = ids[t * top + k];
-        if (e < E) rows_dot<TW>(w_down + (int64_t)n0 * E * F + (int64_t)e * F, (int64_t)E * F, rows, hs + k * F, F, lane, acc);
+        if (e < E) rows_dot<TW, R, U, 1>(w_down + (int64_t)n0 * E * F + (int64_t)e * F, 0, (int64_t)E * F, rows, hs + k * F, F, lane, acc);
     }
 #pragma unroll
-    for (int r = 0; r < MOE_ROWS_PER_WARP; ++r) {
+    for (int r = 0; r < R; ++r) {
         const float v = warp_sum(acc[r]);
         if (lane == 0 && r < rows) out[(int64_t)t * h + n0 + r] = v;
     }
+}
+
+template <typename TA, typename TW, int R, int U>
+static int launch_pairs_as(const void* x, const void* w_up, const void* w_down, const int* ids, const float* wts, void* hid, float* out,
+                           int T, int h, int E, int F, int top, int kind, int gated, int threads, cudaStream_t stream) {
+    const int rows = (threads / 32) * R;
+    const size_t smem_up = (size_t)h * sizeof(float), smem_down = (size_t)top * F * sizeof(float);
+    cudaError_t e = cudaFuncSetAttribute(moe_pairs_up_kernel<TA, TW, R, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(moe_pairs_down_kernel<TA, TW, R, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
+    if (e != cudaSuccess) return (int)e;
+    int rc = launch_kernel(moe_pairs_up_kernel<TA, TW, R, U>, dim3(T * top, (F + rows - 1) / rows), dim3(threads), smem_up, stream,
+                           (const TA*)x, (const TW*)w_up, ids, wts, (TA*)hid, h, E, F, top, kind, gated);
+    if (rc != 0) return rc;
+    return launch_kernel(moe_pairs_down_kernel<TA, TW, R, U>, dim3(T, (h + rows - 1) / rows), dim3(threads), smem_down, stream,
+                         (const TA*)hid, (const TW*)w_down, ids, out, h, E, F, top);
 }
 
 template <typename TA, typename TW>
 static int launch_pairs(const void* x, const void* w_up, const void* w_down, const int* ids, const float* wts, void* hid, float* out,
                         int T, int h, int E, int F, int top, int kind, int gated, cudaStream_t stream) {
     // fewer warps a block where a handful of tokens would leave SMs without one (the warps' work does not depend on it)
-    const int threads = (int64_t)T * ((h + 31) / 32) < 2 * device_sm_count() ? 128 : 256, rows = (threads / 32) * MOE_ROWS_PER_WARP;
-    const size_t smem_up = (size_t)h * sizeof(float), smem_down = (size_t)top * F * sizeof(float);
-    cudaError_t e = cudaFuncSetAttribute(moe_pairs_up_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
-    if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(moe_pairs_down_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
-    if (e != cudaSuccess) return (int)e;
-    int rc = launch_kernel(moe_pairs_up_kernel<TA, TW>, dim3(T * top, (F + rows - 1) / rows), dim3(threads), smem_up, stream, (const TA*)x,
-                           (const TW*)w_up, ids, wts, (TA*)hid, h, E, F, top, kind, gated);
-    if (rc != 0) return rc;
-    return launch_kernel(moe_pairs_down_kernel<TA, TW>, dim3(T, (h + rows - 1) / rows), dim3(threads), smem_down, stream, (const TA*)hid,
-                         (const TW*)w_down, ids, out, h, E, F, top);
+    const int threads = (int64_t)T * ((h + 31) / 32) < 2 * device_sm_count() ? 128 : 256;
+    // the output rows of the smaller of the two products, four a warp: under 12 warps an SM the narrow form (measured at width
+    // 2,048, four experts of 960 a token: one token 52 against 64 us, eight tokens 94 against 81 us)
+    const int64_t quads = (int64_t)T * ((h < (int64_t)top * F ? h : top * F) / 4);
+    if (quads < 12 * (int64_t)device_sm_count())
+        return launch_pairs_as<TA, TW, 1, 4>(x, w_up, w_down, ids, wts, hid, out, T, h, E, F, top, kind, gated, threads, stream);
+    return launch_pairs_as<TA, TW, 4, 1>(x, w_up, w_down, ids, wts, hid, out, T, h, E, F, top, kind, gated, threads, stream);
 }
 
 // Whether the pair kernels take these sizes: rows of whole 16-byte pieces, and a token's hidden rows within shared memory.

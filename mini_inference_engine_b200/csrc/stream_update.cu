@@ -34,6 +34,9 @@ __global__ void normed_add_kernel(float* __restrict__ res, Addend b0, Addend b1,
     const int64_t base = (int64_t)t * W;
     const bool normed = num_addends > 0 || scaled.p != nullptr;
     float r = 0.f;
+    // the thread's first piece of the stream is asked for before the statistics, so that its latency hides under them
+    float4 x_first = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (VEC == 4 && threadIdx.x * 4 < W) x_first = *reinterpret_cast<const float4*>(res + base + threadIdx.x * 4);
     if (normed) {
         const float rs = scaled.p ? row_scale[t] : 0.f;
         float ss = 0.f;
@@ -63,7 +66,7 @@ __global__ void normed_add_kernel(float* __restrict__ res, Addend b0, Addend b1,
     }
     if (VEC == 4) {
         for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
-            float4 x = *reinterpret_cast<const float4*>(res + base + i);
+            float4 x = i == threadIdx.x * 4 ? x_first : *reinterpret_cast<const float4*>(res + base + i);
             if (normed) {
                 const float4 y = *reinterpret_cast<const float4*>(ys + i);
                 float4 v = make_float4(r, r, r, r);
