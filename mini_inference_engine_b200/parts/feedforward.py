@@ -224,21 +224,46 @@ class RoutedExperts(FeedForward):
         return {"moe", "gemm_simt"} | self.rt.product_sources(self.w_up, self.w_down) | shared      # (gemm_simt: the router of a very wide model)
 
     def forward(self, x, ctx):
-        if x.is_contiguous() and (self.hidden_size + self.outputs) * 4 <= 200 * 1024:
+        """The chosen experts and the shared expert depend on nothing of one another.  For a handful of tokens both are short
+        chains of kernels at a launch's latency each (router and the two pair kernels here, two or three launches there), so
+        the shared expert runs on a stream of its own between a fork and a join (events; two arms of the graph inside a
+        captured step) and the two chains take the time of one.  Only beside the pair kernels, which use no products of the
+        runtime: the shared expert's products then have the runtime's kernels to themselves.  Every tensor either arm makes
+        is used by the main stream only after the join, and the side stream starts only after the fork, so the allocator's
+        per-stream reuse stays ordered."""
+        from . import parallel
+        shared = join = None
+        one_kernel_router = x.is_contiguous() and (self.hidden_size + self.outputs) * 4 <= 200 * 1024
+        if self.shared is not None and parallel.SIDE_BY_SIDE_STREAMS and x.is_cuda and one_kernel_router and self._pairs_serve(x):
+            main, side = torch.cuda.current_stream(), parallel._side_stream(x.device)
+            fork, join = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                shared = self.shared.forward(x, ctx)
+                join.record(side)
+        if one_kernel_router:
             routed = ops.moe_router(x, self.w_router, self.top, rule=self.rule)          # logits, choice and weights in one kernel
         else:
             routed = ops.moe_route(self.rt.linear(x, self.w_router, None, out_dtype=torch.float32), self.top, self.rule)
         out = self._experts(x, routed[0], routed[1])
         if self.shared is None and len(routed) == 2:
             return out
+        if join is not None:
+            torch.cuda.current_stream().wait_event(join)
+        elif self.shared is not None:
+            shared = self.shared.forward(x, ctx)
         from .block import Branches
-        deltas = [out] + ([self.shared.forward(x, ctx)] if self.shared is not None else [])
-        return Branches(deltas, scaled=(x, routed[2]) if len(routed) == 3 else None)
+        return Branches([out] + ([shared] if shared is not None else []), scaled=(x, routed[2]) if len(routed) == 3 else None)
+
+    def _pairs_serve(self, x) -> bool:
+        return (x.shape[0] * self.top <= self.num_experts and x.is_contiguous()
+                and (x.dtype == self.w_up.dtype or self.w_up.dtype == torch.float32)
+                and ops.moe_pairs_fit(self.hidden_size, self.expert_size, self.top))
 
     def _experts(self, x, ids, wts):
         T = x.shape[0]
-        if (T * self.top <= self.num_experts and x.is_contiguous() and (x.dtype == self.w_up.dtype or self.w_up.dtype == torch.float32)
-                and ops.moe_pairs_fit(self.hidden_size, self.expert_size, self.top)):
+        if self._pairs_serve(x):
             out = torch.empty(T, self.hidden_size, dtype=torch.float32, device=x.device)
             return ops.moe_pairs(x, self.w_up, self.w_down, ids, wts, out, self.num_experts, self.activation, self.gated)
         # up to the token count that the framework's own streaming product serves, the wide form reads every expert once at
