@@ -91,6 +91,65 @@ __device__ __forceinline__ void route_scored(const float* zt, int* ids, float* w
     if (rest) *rest = idw;
 }
 
+// Mode 1 for one token by a whole warp: zt holds the softmax scores (shared memory, made by this warp).  The same choice as
+// route_scored, outcome for outcome: a group is kept if fewer than `keep` groups come before it in the order (value falling,
+// index rising), which is what picking the best group `keep` times gives; each of the `top` picks is a maximum over the lanes'
+// own outputs and then over the lanes, ties to the lower index.  A thread alone walks these loops at a dependent instruction
+// every few cycles (16 us of a 26 us launch for one token, twenty outputs, four groups); a warp takes a few hundred cycles.
+__device__ __forceinline__ void route_scored_warp(const float* zt, int* ids, float* wts, int n, int top, const RouteRule& rr, float* rest,
+                                                  int lane) {
+    const unsigned full = 0xffffffffu;
+    auto choice = [&](int e) { return rr.correction ? zt[e] + rr.correction[e] : zt[e]; };
+    unsigned long long allowed = ~0ull;
+    const int per = rr.groups > 1 ? n / rr.groups : n;
+    if (rr.groups > 1 && rr.keep < rr.groups) {             // at most 64 groups: a lane holds groups lane and lane + 32
+        float v[2];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int g = lane + 32 * r;
+            float m = -INFINITY;
+            if (g < rr.groups)
+                for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, choice(e));
+            v[r] = m;
+        }
+        int ahead[2] = {0, 0};
+        for (int g2 = 0; g2 < rr.groups; ++g2) {
+            const float o = __shfl_sync(full, g2 < 32 ? v[0] : v[1], g2 & 31);
+#pragma unroll
+            for (int r = 0; r < 2; ++r)
+                if (o > v[r] || (o == v[r] && g2 < lane + 32 * r)) ++ahead[r];
+        }
+        const unsigned lo = __ballot_sync(full, lane < rr.groups && ahead[0] < rr.keep);
+        const unsigned hi = __ballot_sync(full, lane + 32 < rr.groups && ahead[1] < rr.keep);
+        allowed = (unsigned long long)lo | ((unsigned long long)hi << 32);
+    }
+    float prev_v = INFINITY, idw = 0.f;
+    int prev_i = -1;
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int bi = -1;
+        for (int e = lane; e < n; e += 32) {
+            if (!((allowed >> (rr.groups > 1 ? e / per : 0)) & 1ull)) continue;
+            const float c = choice(e);
+            const bool after_prev = c < prev_v || (c == prev_v && e > prev_i);
+            if (after_prev && (bi < 0 || c > best)) { best = c; bi = e; }
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+            const float ob = __shfl_xor_sync(full, best, off);
+            const int oi = __shfl_xor_sync(full, bi, off);
+            if (oi >= 0 && (bi < 0 || ob > best || (ob == best && oi < bi))) { best = ob; bi = oi; }
+        }
+        float w = 0.f;
+        if (bi < 0) bi = 0; else w = zt[bi];                  // scores that are not numbers: keep the ids in range, weight 0
+        if (lane == 0) { ids[k] = bi; wts[k] = w; }
+        if (bi >= rr.real) idw += w;
+        prev_v = best;
+        prev_i = bi;
+    }
+    if (rest && lane == 0) *rest = idw;
+}
+
 // The `top` largest of zt[0 .. E) in order (ties: the lower index first) and the softmax over them.
 __device__ __forceinline__ void route_one(const float* zt, int* ids, float* wts, int E, int top) {
     float prev_v = INFINITY;
@@ -148,7 +207,8 @@ static __host__ __device__ inline int router_segments(int E, int h, int warps) {
 
 // A block per ROUTER_TOKENS tokens: their inputs into shared memory as float32, a warp per (output, column segment) in turn
 // for the logits of all of them (the output's row is read once a block), the segments' sums added in their order, then a
-// warp per token for the scores and a thread per token chooses.  `logits` (optional) receives z.
+// warp per token for the scores and, by the second rule, the choice (by the first rule a thread per token chooses).  `logits`
+// (optional) receives z.
 template <typename TA>
 __global__ void __launch_bounds__(ROUTER_THREADS)
 moe_router_kernel(const TA* __restrict__ x, const float* __restrict__ w, int* __restrict__ ids, float* __restrict__ wts,
@@ -234,12 +294,15 @@ moe_router_kernel(const TA* __restrict__ x, const float* __restrict__ w, int* __
             sum = warp_sum(sum);
             __syncwarp();
             for (int e = lane; e < E; e += 32) z[i * E + e] /= sum;
+            __syncwarp();
+            route_scored_warp(z + i * E, ids + (int64_t)(t0 + i) * top, wts + (int64_t)(t0 + i) * top, E, top, rr,
+                              rr.rest ? rr.rest + t0 + i : nullptr, lane);
         }
-        __syncthreads();
+        return;
     }
     if (threadIdx.x < nt)
         route_by_rule(z + threadIdx.x * E, ids + (int64_t)(t0 + threadIdx.x) * top, wts + (int64_t)(t0 + threadIdx.x) * top, E, top, rr,
-                      rr.mode == 1, t0 + threadIdx.x);
+                      false, t0 + threadIdx.x);
 }
 
 __device__ __forceinline__ float expert_act(float x, int kind) {
