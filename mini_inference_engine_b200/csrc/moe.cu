@@ -377,6 +377,22 @@ __device__ __forceinline__ void rows_dot(const TW* __restrict__ first, int64_t g
     }
 }
 
+// n entries (a multiple of 8) of a row into shared memory as float32 by the whole block, 16 bytes a load where the row allows:
+// a thread's loads do not depend on one another, so they are in flight together.
+template <typename TA>
+__device__ __forceinline__ void fill_f32(float* __restrict__ dst, const TA* __restrict__ src, int n) {
+    if ((reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        for (int c = threadIdx.x * 8; c < n; c += blockDim.x * 8) {
+            float v[8];
+            load8<TA>(src + c, v);
+            *reinterpret_cast<float4*>(dst + c) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(dst + c + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        }
+    } else {
+        for (int c = threadIdx.x; c < n; c += blockDim.x) dst[c] = to_f32<TA>(src[c]);
+    }
+}
+
 // R rows a warp and U column steps at a time: (4, 1) where the batch gives every SM its fill of warps, (1, 4) for a handful of
 // tokens, where more and narrower warps keep as many bytes in flight.  A row's sum runs over its columns in the same order
 // either way, so the result does not depend on the choice.
@@ -390,7 +406,7 @@ __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restri
     const int e = ids[pair];
     const float weight = wts[pair];
     if (e >= E) return;                                        // an identity expert: the down kernel skips the pair
-    for (int c = threadIdx.x; c < h; c += blockDim.x) xs[c] = to_f32<TA>(x[(int64_t)t * h + c]);
+    fill_f32<TA>(xs, x + (int64_t)t * h, h);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int f0 = (blockIdx.y * nw + warp) * R, rows = min(R, F - f0);
@@ -415,8 +431,8 @@ __global__ void moe_pairs_down_kernel(const TA* __restrict__ hid, const TW* __re
     extern __shared__ __align__(16) float hs[];               // the token's `top` hidden rows, float32 [top, F]
     pdl_enter();
     const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < top * F; c += blockDim.x)
-        hs[c] = ids[t * top + c / F] < E ? to_f32<TA>(hid[(int64_t)t * top * F + c]) : 0.f;
+    for (int k = 0; k < top; ++k)                             // an identity expert's row is never read: the loop below skips it
+        if (ids[t * top + k] < E) fill_f32<TA>(hs + k * F, hid + ((int64_t)t * top + k) * F, F);
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     const int n0 = (blockIdx.y * nw + warp) * R, rows = min(R, h - n0);
