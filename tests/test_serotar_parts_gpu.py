@@ -437,3 +437,43 @@ def test_a_key_far_back_that_stands_out(dt, far):
     close(run_in_portions(h, x, [T]), want, dt, "whole")
     close(run_in_portions(h, x, [T - 5, 2, 1, 1, 1]), want, dt, "the last queries decoded alone")
     close(run_in_portions(h, x, [7, 9, 1, 15, 2, 200, 61, 3, 2]), want, dt, "portions cut inside pages")
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("gated", [True, False])
+def test_pair_kernels_give_a_token_the_same_sums_in_a_small_and_in_a_large_batch(dt, gated):
+    """The experts' kernels for single (token, expert) pairs come in two forms, chosen by the size of the batch: one row a warp
+    and four column steps at a time, or four rows a warp.  Both against the plain sum, and a token's result must be the same
+    number for number whichever form its batch got: a row's sum runs over its columns in one order."""
+    from mini_inference_engine_b200.kernels import ops
+    g = torch.Generator().manual_seed(11)
+    h, F, E, top, identity = 512, 136, 12, 4, 3
+    wu = (torch.randn(E * (2 if gated else 1) * F, h, generator=g) * h ** -0.5).to(dt)
+    wd = (torch.randn(h, E * F, generator=g) * F ** -0.5).to(dt)
+    x = torch.randn(48, h, generator=g).to(dt)
+    ids = torch.stack([torch.randperm(E + identity, generator=g)[:top] for _ in range(48)]).to(torch.int32)
+    wts = torch.rand(48, top, generator=g) + 0.1
+    want = torch.zeros(48, h, dtype=torch.float64)
+    for t in range(48):
+        for e, w in zip(ids[t].tolist(), wts[t].tolist()):
+            if e >= E:
+                continue                                   # an identity expert: the pair kernels add nothing for it
+            if gated:
+                gate = wu[e * 2 * F:e * 2 * F + F].double() @ x[t].double()
+                up = wu[e * 2 * F + F:(e + 1) * 2 * F].double() @ x[t].double()
+                hid = w * torch.nn.functional.silu(gate) * up
+            else:
+                hid = w * torch.nn.functional.silu(wu[e * F:(e + 1) * F].double() @ x[t].double())
+            if dt == torch.bfloat16:
+                hid = hid.to(dt).double()                  # the hidden row is stored in the activation type
+            want[t] += wd[:, e * F:(e + 1) * F].double() @ hid
+    outs = {}
+    for T in (1, 2, 5, 48):                                # 48 tokens of 512: four rows a warp; the others: one row
+        out = torch.empty(T, h, dtype=torch.float32, device=DEV)
+        ops.moe_pairs(x[:T].contiguous().to(DEV), wu.to(DEV), wd.to(DEV), ids[:T].contiguous().to(DEV), wts[:T].contiguous().to(DEV), out, E,
+                      "silu", gated=gated)
+        outs[T] = out.cpu()
+        tol = 2e-2 if dt == torch.bfloat16 else 1e-4
+        assert (outs[T].double() - want[:T]).abs().max().item() <= tol * want.abs().max().item(), (T, dt, gated)
+    for T in (1, 2, 5):
+        assert torch.equal(outs[T], outs[48][:T]), f"a token's sums differ between a batch of {T} and a batch of 48"
