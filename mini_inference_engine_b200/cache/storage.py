@@ -33,14 +33,19 @@ class CacheLayout:
         """``needs[cache id]`` is what the mixer that uses it declared (None, KVNeed or StateNeed)."""
         lay = cls()
         # a mixer made of several declares a tuple of needs: entry i of cache id c is stored under (c, i)
+        # (an entry may be a tuple again -- mixers side by side, one of them with several states: stored under ((c, i), j))
         flat = {}
-        for layer, n in needs.items():
+
+        def add(key, n):
             if isinstance(n, (tuple, list)):
-                lay.composite[layer] = len(n)
+                lay.composite[key] = len(n)
                 for i, m in enumerate(n):
-                    flat[(layer, i)] = m
+                    add((key, i), m)
             else:
-                flat[layer] = n
+                flat[key] = n
+
+        for layer, n in needs.items():
+            add(layer, n)
         kinds = sorted({(n.window, n.chunk) for n in flat.values() if isinstance(n, KVNeed)},
                        key=lambda wc: (wc[0] is not None, wc[0] or 0, wc[1] is not None, wc[1] or 0))
         index = {}

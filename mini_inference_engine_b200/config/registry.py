@@ -6,6 +6,7 @@ from __future__ import annotations
 
 from .getizen_config import GetizenConfig
 from .kebudra_config import KebudraConfig
+from .luluzen_config import LuluzenConfig
 from .serotar_config import SerotarConfig
 from .model_config import ConfigError, LlamaConfig, read_config_json
 
@@ -44,6 +45,7 @@ register_architecture("LlamaForCausalLM", LlamaConfig)
 register_architecture("Getizen", GetizenConfig)
 register_architecture("Kebudra", KebudraConfig)
 register_architecture("Serotar", SerotarConfig)
+register_architecture("Luluzen", LuluzenConfig)
 
 
 def preset_names() -> list[str]:

@@ -87,7 +87,8 @@ extern "C" int mie_swiglu(const void* gu, void* out, int act_tag, int num_tokens
 // A gated feed-forward activation with clamps, on a fused projection [gate | up] (gate first, `inter` columns each; with
 // `interleaved`, columns alternate gate_i, up_i as for SwiGLU above):
 //   g = min(gate, limit), u = clamp(up, -limit, limit);  out = g * sigmoid(slope * g) * (u + shift)
-// computed in float32 and rounded once.  limit <= 0 means no clamp.
+// computed in float32 and rounded once.  limit <= 0 means no clamp; limit < 0 also puts a cubic term into the sigmoid's
+// argument, slope * g * (1 - limit * g^2): with slope 2 sqrt(2/pi) and limit -0.044715 the gate is gelu in its tanh form.
 template <typename T>
 __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int inter, float limit,
                                    float slope, float shift, int interleaved) {
@@ -99,7 +100,8 @@ __global__ void glu_clamped_kernel(const T* __restrict__ gu, T* __restrict__ out
         float g = to_f32<T>(gu[t * 2 * inter + (interleaved ? 2 * i : i)]);
         float u = to_f32<T>(gu[t * 2 * inter + (interleaved ? 2 * i + 1 : inter + i)]);
         if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
-        out[idx] = from_f32<T>(g / (1.0f + expf(-slope * g)) * (u + shift));
+        const float z = limit < 0.f ? slope * g * fmaf(-limit * g, g, 1.0f) : slope * g;
+        out[idx] = from_f32<T>(g / (1.0f + expf(-z)) * (u + shift));
     }
 }
 
@@ -133,8 +135,10 @@ __global__ void glu_clamped_bf16x8_kernel(const bf16* __restrict__ gu, bf16* __r
                 g.x = fminf(g.x, limit); g.y = fminf(g.y, limit);
                 u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
             }
-            ho[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-slope * g.x)) * (u.x + shift),
-                                          __fdividef(g.y, 1.0f + __expf(-slope * g.y)) * (u.y + shift));
+            float2 z = make_float2(slope * g.x, slope * g.y);
+            if (limit < 0.f) { z.x *= fmaf(-limit * g.x, g.x, 1.0f); z.y *= fmaf(-limit * g.y, g.y, 1.0f); }
+            ho[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-z.x)) * (u.x + shift),
+                                          __fdividef(g.y, 1.0f + __expf(-z.y)) * (u.y + shift));
         }
         *reinterpret_cast<uint4*>(out + idx * 8) = o;
     }

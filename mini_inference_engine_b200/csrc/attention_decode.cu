@@ -48,12 +48,13 @@ extern "C" int mie_decode_attention(const void* q, int64_t q_stride, const void*
                                     int num_heads, int num_kv_heads, int head_dim, int page_size, float scale,
                                     int window, int splits, float* part_o, float* part_lse, int* counters,
                                     int stages, int64_t num_pages, int64_t check_pages, int min_part_tiles,
-                                    const float* cos_t, const float* sin_t, int max_pos, int out_f32,
-                                    cudaStream_t stream) {
+                                    const float* cos_t, const float* sin_t, int max_pos, int out_f32, float softcap,
+                                    const float* sink, const float* dist_bias, int dist_len, cudaStream_t stream) {
+    const ScoreMods mods{softcap, sink, dist_bias, dist_len};
     return decode_attention_launch(q, q_stride, k_cache, v_cache, block_tables, table_stride, row_q_start, row_q_len,
                                    row_ctx_len, num_rows, out, num_heads, num_kv_heads, head_dim, page_size, scale,
                                    window, splits, part_o, part_lse, counters, stream, stages, num_pages, check_pages,
-                                   g_range_report, min_part_tiles, cos_t, sin_t, max_pos, out_f32 != 0);
+                                   g_range_report, min_part_tiles, cos_t, sin_t, max_pos, out_f32 != 0, &mods);
 }
 
 // Non-zero when a block of any launch so far gave up a bounded wait (TMA copies that did not arrive).

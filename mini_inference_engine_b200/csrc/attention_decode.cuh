@@ -35,6 +35,9 @@ struct DecodeParams {
     // rotated by the token's position ctx - 1 with the whole head as rotary width (D % 32 == 0), and the block
     // whose part holds that position writes key and value into the cache (the block of the first chunk of heads).
     const float* cos_t; const float* sin_t; int max_pos;
+    float scale;             // the scale without the base-2 factor, for scores that are modified before the softmax
+    ScoreMods mods;          // cap, bias by distance, sink (common.cuh); all off: the plain softmax
+    int modded;
 };
 
 // Where the 16-byte piece `chunk` of key row `row` lies inside a tile that TMA wrote with the
@@ -130,6 +133,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
     for (int n = 0; n < NBLK; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (p.mods.sink && split == 0 && warp == 0) {                  // the sink joins the sum once: in one warp of the row's first part
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+            if (quad + 8 * h < gn) { m[h] = p.mods.sink[kvh * G + g0 + quad + 8 * h] * 1.4426950408889634f; l[h] = 1.f; }
+    }
 
     volatile int* abort_p = &abort_flag;
     if (TMA) {
@@ -310,6 +318,11 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float v = s[n][i] * p.scale_log2e;
+                    if (p.modded) {
+                        const int gi = min(quad + 8 * (i >> 1), gn - 1);      // rows beyond the group's heads are never written
+                        v = mod_score(s[n][i] * p.scale, p.mods, kvh * G + g0 + gi, p.num_heads,
+                                      ctx - 1 - (key0 + n * 8 + tq * 2 + (i & 1))) * 1.4426950408889634f;
+                    }
                     if (!whole) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
                         if (!(key < kend && key >= first_key)) v = -INFINITY;
@@ -576,7 +589,8 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
                                    int window, int splits, float* part_o, float* part_lse, int* counters,
                                    cudaStream_t stream, int stages = 0, int64_t num_pages = 0,
                                    int64_t check_pages = 0, int* report = nullptr, int min_part_tiles = 0,
-                                   const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, bool out_f32 = false) {
+                                   const float* cos_t = nullptr, const float* sin_t = nullptr, int max_pos = 0, bool out_f32 = false,
+                                   const ScoreMods* mods = nullptr) {
     if (num_rows <= 0) return 0;
     if (head_dim < 16 || head_dim > DEC_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
@@ -600,6 +614,10 @@ static int decode_attention_launch(const void* q, int64_t q_stride, const void* 
     const int G = num_heads / num_kv_heads;
     p.chunks = (G + 15) / 16;
     p.scale_log2e = scale * 1.4426950408889634f;
+    p.scale = scale;
+    p.mods = mods ? *mods : ScoreMods{0.f, nullptr, nullptr, 0};
+    if (p.mods.dist_bias && p.mods.dist_len <= 0) return MIE_ERR_BAD_ARG;
+    p.modded = p.mods.softcap > 0.f || p.mods.dist_bias != nullptr;
     p.check_pages = check_pages; p.report = report;
     if ((cos_t != nullptr) != (sin_t != nullptr) || (cos_t && (head_dim % 32 || max_pos <= 0))) return MIE_ERR_BAD_ARG;
     p.cos_t = cos_t; p.sin_t = sin_t; p.max_pos = max_pos;

@@ -32,6 +32,9 @@ struct PrefillParams {
     float scale_log2e;
     int64_t check_pages;     // pages in each cache, for the range check of block-table entries
     int* report;             // range report (range_check.cuh)
+    float scale;             // the same scale without the base-2 factor, for scores that are modified before the softmax
+    ScoreMods mods;          // cap, bias by distance, sink (common.cuh); all off: the plain softmax
+    int modded;
 };
 
 template <int D>
@@ -90,6 +93,10 @@ prefill_attention_kernel(const PrefillParams p) {
 #pragma unroll
     for (int n = 0; n < NBLK; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    if (p.mods.sink) {                                              // the sink: one more term of every row's sum, with no value
+        m[0] = m[1] = p.mods.sink[head] * 1.4426950408889634f;
+        l[0] = l[1] = 1.f;
+    }
 
     // page ids go to shared memory first: a look-up in global memory inside the tile loop would put a
     // memory round trip in front of every tile's copies
@@ -156,6 +163,8 @@ prefill_attention_kernel(const PrefillParams p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float v = s[n][i] * p.scale_log2e;
+                    if (p.modded)
+                        v = mod_score(s[n][i] * p.scale, p.mods, head, p.num_heads, qpos[i >> 1] - (key0 + n * 8 + tq * 2 + (i & 1))) * 1.4426950408889634f;
                     if (need_mask) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
                         const int qp = qpos[i >> 1];
@@ -251,7 +260,8 @@ extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void
                                      const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens,
                                      void* out, int num_heads, int num_kv_heads, int head_dim, int page_size,
                                      float scale, int window, int min_q_len, long long num_pages, int work_rows,
-                                     int work_tokens, int out_f32, cudaStream_t stream) {
+                                     int work_tokens, int out_f32, float softcap, const float* sink, const float* dist_bias,
+                                     int dist_len, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (work_rows <= 0 || work_tokens <= 0 || work_rows > num_rows || work_tokens > num_tokens) { work_rows = num_rows; work_tokens = num_tokens; }
     if (head_dim < 16 || head_dim > PRE_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
@@ -269,6 +279,10 @@ extern "C" int mie_prefill_attention(const void* q, int64_t q_stride, const void
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.min_q_len = min_q_len;
     p.scale_log2e = scale * 1.4426950408889634f;
+    if (dist_bias && dist_len <= 0) return MIE_ERR_BAD_ARG;
+    p.scale = scale;
+    p.mods = ScoreMods{softcap, sink, dist_bias, dist_len};
+    p.modded = softcap > 0.f || dist_bias != nullptr;
     p.check_pages = num_pages > 0 ? (int64_t)num_pages : ((int64_t)1 << 40); p.report = g_range_report;
     switch (head_dim) {
         case 16: return launch_prefill<16>(p, work_tokens, work_rows, stream);

@@ -6,7 +6,8 @@
 // cache, ctx_len = tokens in the cache including them.  Query i of the row sits at position
 // p = ctx_len - q_len + i and reads keys j <= p (from mask_first_key(p, window) on: a sliding window or its own block of positions) through the
 // row's block table.  Query head h reads kv head h / (H / H_kv).  Scores, softmax and the
-// accumulator are float32; online softmax over tiles of 32 keys.
+// accumulator are float32; online softmax over tiles of 32 keys.  A score may be capped, take a bias by distance and share
+// the softmax with a sink (ScoreMods, common.cuh).
 //
 // This replaces the reference's three code paths (Triton decode kernel for single tokens,
 // SDPA on local k/v for a fresh prompt, SDPA on gathered k/v + mask for a continued one,
@@ -52,7 +53,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
                        const int* __restrict__ row_q_len, const int* __restrict__ row_ctx_len,
                        int num_rows, TO* __restrict__ out, int num_heads, int num_kv_heads,
                        int head_dim, int page_size, int page_shift, float scale, int window,
-                       int QT, int HG, int min_q_len, int64_t num_pages, int* report) {
+                       int QT, int HG, int min_q_len, int64_t num_pages, int* report, const ScoreMods mods) {
     extern __shared__ __align__(16) float smem[];
     __shared__ int s_row, s_q0;
     const int D = head_dim, DP = head_dim + 4;
@@ -100,6 +101,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
     const int k_lo = mask_first_key(ctx_len - q_len + q0, window);
 
     float m = -INFINITY, l = 0.f;
+    if (active && mods.sink) { m = mods.sink[head]; l = 1.f; }      // the sink: one more term of the sum, with no value
     float acc[ATT_MAX_D / 32];
 #pragma unroll
     for (int i = 0; i < ATT_MAX_D / 32; ++i) acc[i] = 0.f;
@@ -137,7 +139,7 @@ paged_attention_kernel(const T* __restrict__ q, int64_t q_stride, const T* __res
                 const float4 a = qr[d4], b = kr[d4];
                 s = fmaf(a.x, b.x, s); s = fmaf(a.y, b.y, s); s = fmaf(a.z, b.z, s); s = fmaf(a.w, b.w, s);
             }
-            s = valid ? s : -INFINITY;
+            s = valid ? mod_score(s, mods, head, num_heads, pos_q - key) : -INFINITY;
             const float m_new = fmaxf(m, warp_max(s));
             if (m_new > -INFINITY) {           // else every key of this tile is masked for this query
                 const float alpha = expf(m - m_new);          // m = -inf gives 0
@@ -181,9 +183,12 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
                                    const int* row_q_len, const int* row_ctx_len, int num_rows,
                                    int num_tokens, void* out, int act_tag, int num_heads, int num_kv_heads,
                                    int head_dim, int page_size, float scale, int window, int min_q_len,
-                                   long long num_pages, int out_f32, cudaStream_t stream) {
+                                   long long num_pages, int out_f32, float softcap, const float* sink, const float* dist_bias,
+                                   int dist_len, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (head_dim < 16 || head_dim > ATT_MAX_D || head_dim % 16) return MIE_ERR_BAD_ARG;
+    if (dist_bias && dist_len <= 0) return MIE_ERR_BAD_ARG;
+    const ScoreMods mods{softcap, sink, dist_bias, dist_len};
     if (num_kv_heads <= 0 || num_heads % num_kv_heads) return MIE_ERR_BAD_ARG;
     if (page_size < 1 || (page_size & (page_size - 1))) return MIE_ERR_BAD_ARG;
     int page_shift = 0;
@@ -201,21 +206,21 @@ extern "C" int mie_paged_attention(const void* q, int64_t q_stride, const void* 
         return launch_kernel(paged_attention_kernel<float, float>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const float*)q, q_stride, (const float*)k_cache, (const float*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (float*)out, num_heads, num_kv_heads, head_dim,
-            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);
+            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report, mods);
     } else if (act_tag == MIE_BF16 && out_f32) {             // bfloat16 operands, the output left in float32
         e = cudaFuncSetAttribute(paged_attention_kernel<bf16, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         return launch_kernel(paged_attention_kernel<bf16, float>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (float*)out, num_heads, num_kv_heads, head_dim,
-            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);
+            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report, mods);
     } else if (act_tag == MIE_BF16) {
         e = cudaFuncSetAttribute(paged_attention_kernel<bf16, bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         return launch_kernel(paged_attention_kernel<bf16, bf16>, grid, dim3(ATT_WARPS * 32), smem, stream,
             (const bf16*)q, q_stride, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, table_stride,
             row_q_start, row_q_len, row_ctx_len, num_rows, (bf16*)out, num_heads, num_kv_heads, head_dim,
-            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report);
+            page_size, page_shift, scale, window, QT, HG, min_q_len, (int64_t)num_pages, g_range_report, mods);
     }
     return MIE_ERR_BAD_ARG;
 }

@@ -26,6 +26,19 @@ __host__ __device__ __forceinline__ int mask_first_key(int pos, int window) {
     return 0;
 }
 
+// What may happen to an attention score between the scaled product q . k and the softmax, each switched by its field:
+struct ScoreMods {
+    float softcap;             // > 0: s <- softcap * tanh(s / softcap)
+    const float* sink;         // not null, [heads]: exp(sink[head]) joins the softmax's denominator once (it has no key and no value)
+    const float* dist_bias;    // not null, [dist_len, heads]: the query at position p adds row min(p - j, dist_len - 1) to key j's score
+    int dist_len;
+};
+__device__ __forceinline__ float mod_score(float s, const ScoreMods& m, int head, int num_heads, int dist) {
+    if (m.softcap > 0.f) s = m.softcap * tanhf(s / m.softcap);
+    if (m.dist_bias) s += m.dist_bias[(int64_t)min(max(dist, 0), m.dist_len - 1) * num_heads + head];
+    return s;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }

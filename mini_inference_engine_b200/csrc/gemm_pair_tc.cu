@@ -261,7 +261,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                     for (int i = 0; i < 16; ++i) {
                         float g = v[2 * i], u = v[2 * i + 1];
                         if (p.glu_limit > 0.f) { g = fminf(g, p.glu_limit); u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit); }
-                        o[i] = __fdividef(g, 1.f + __expf(-p.glu_slope * g)) * (u + p.glu_shift);
+                        const float z = p.glu_limit < 0.f ? p.glu_slope * g * fmaf(-p.glu_limit * g, g, 1.f) : p.glu_slope * g;     // limit < 0: the cubic term
+                        o[i] = __fdividef(g, 1.f + __expf(-z)) * (u + p.glu_shift);
                     }
                     const int64_t at = (int64_t)row * (p.N / 2) + col / 2;
                     if (p.out_f32) {

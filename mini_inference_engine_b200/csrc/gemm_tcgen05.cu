@@ -133,11 +133,12 @@ __device__ __forceinline__ void store_row16(void* out, int64_t row_off, int n, i
 
 __device__ __forceinline__ void grid_dep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// the gated epilogue g sigmoid(slope g) (u + shift), clamped, with the fast exponential and division (a few ulp; the result is rounded to bfloat16 or
+// the gated epilogue g sigmoid(slope g) (u + shift), clamped (limit > 0) or with the sigmoid's argument slope g (1 - limit g^2) (limit < 0), with the fast exponential and division (a few ulp; the result is rounded to bfloat16 or
 // added to float32 sums of bfloat16 products)
 __device__ __forceinline__ float glu_mul(float g, float u, float limit, float slope, float shift) {
     if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
-    return __fdividef(g, 1.0f + __expf(-slope * g)) * (u + shift);
+    const float z = limit < 0.f ? slope * g * fmaf(-limit * g, g, 1.0f) : slope * g;      // a negative limit: no clamp, -limit the cubic term (gelu's tanh form)
+    return __fdividef(g, 1.0f + __expf(-z)) * (u + shift);
 }
 #define GLU_OF(g, u) glu_mul(g, u, p.glu_limit, p.glu_slope, p.glu_shift)      // inside a kernel whose parameters are `p`
 

@@ -28,7 +28,8 @@
 #include "common.cuh"
 
 struct RouteRule {
-    int mode;                    // 0: the largest logits, softmax over the chosen; 1: softmax over all, see above
+    int mode;                    // 0: the largest logits, softmax over the chosen; 1: softmax over all, see above;
+                                 // 2: the largest logits, each chosen one's weight its own sigmoid (not renormalized)
     const float* correction;     // [outputs] added for the choice only (mode 1), or null
     int groups, keep;            // groups <= 1 or keep >= groups: no limit
     int real;                    // router outputs below this have matrices; the others are identity experts
@@ -179,6 +180,8 @@ __device__ __forceinline__ void route_by_rule(const float* zt, int* ids, float* 
                                               int64_t t) {
     if (rr.mode == 1) { route_scored(zt, ids, wts, E, top, rr, ready, rr.rest ? rr.rest + t : nullptr); return; }
     route_one(zt, ids, wts, E, top);
+    if (rr.mode == 2)                                          // the sigmoid keeps the logits' order: the same choice, other weights
+        for (int k = 0; k < top; ++k) wts[k] = 1.0f / (1.0f + expf(-zt[ids[k]]));
     if (rr.rest) {
         float idw = 0.f;
         for (int k = 0; k < top; ++k) if (ids[k] >= rr.real) idw += wts[k];
@@ -311,6 +314,16 @@ __device__ __forceinline__ float expert_act(float x, int kind) {
     return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 
+// A gated expert's hidden value from its gate and up sums g, u and the token's weight w.  Kinds 0 - 2: w act(g) u.  Kind 3:
+// the weight multiplies the expert's INPUT (so both sums), and the gate is clamped: with g' = min(w g, limit),
+// u' = clamp(w u, -limit, limit) the value is g' sigmoid(1.702 g') (u' + 1), and nothing multiplies the output.
+__device__ __forceinline__ float gated_value(float g, float u, float w, int kind, float limit) {
+    if (kind != 3) return w * expert_act(g, kind) * u;
+    g *= w; u *= w;
+    if (limit > 0.f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
 template <typename T>
 __global__ void moe_dense_act_kernel(const T* __restrict__ up, const int* __restrict__ ids, const float* __restrict__ wts,
                                      T* __restrict__ act, int64_t total, int E, int F, int top, int kind) {
@@ -399,7 +412,7 @@ __device__ __forceinline__ void fill_f32(float* __restrict__ dst, const TA* __re
 template <typename TA, typename TW, int R, int U>
 __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restrict__ w_up, const int* __restrict__ ids,
                                     const float* __restrict__ wts, TA* __restrict__ hid, int h, int E, int F, int top, int kind,
-                                    int gated) {
+                                    int gated, float limit) {
     extern __shared__ __align__(16) float xs[];               // the token's input, float32
     pdl_enter();
     const int pair = blockIdx.x, t = pair / top;
@@ -420,8 +433,8 @@ __global__ void moe_pairs_up_kernel(const TA* __restrict__ x, const TW* __restri
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const float gs = warp_sum(gu[r]);
-        const float v = gated ? expert_act(gs, kind) * warp_sum(gu[R + r]) : expert_act(gs, kind);
-        if (lane == 0 && r < rows) hid[(int64_t)pair * F + f0 + r] = from_f32<TA>(weight * v);
+        const float v = gated ? gated_value(gs, warp_sum(gu[R + r]), weight, kind, limit) : weight * expert_act(gs, kind);
+        if (lane == 0 && r < rows) hid[(int64_t)pair * F + f0 + r] = from_f32<TA>(v);
     }
 }
 
@@ -453,7 +466,7 @@ __global__ void moe_pairs_down_kernel(const TA* __restrict__ hid, const TW* __re
 
 template <typename TA, typename TW, int R, int U>
 static int launch_pairs_as(const void* x, const void* w_up, const void* w_down, const int* ids, const float* wts, void* hid, float* out,
-                           int T, int h, int E, int F, int top, int kind, int gated, int threads, cudaStream_t stream) {
+                           int T, int h, int E, int F, int top, int kind, int gated, int threads, float limit, cudaStream_t stream) {
     const int rows = (threads / 32) * R;
     const size_t smem_up = (size_t)h * sizeof(float), smem_down = (size_t)top * F * sizeof(float);
     cudaError_t e = cudaFuncSetAttribute(moe_pairs_up_kernel<TA, TW, R, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_up);
@@ -461,7 +474,7 @@ static int launch_pairs_as(const void* x, const void* w_up, const void* w_down, 
     e = cudaFuncSetAttribute(moe_pairs_down_kernel<TA, TW, R, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_down);
     if (e != cudaSuccess) return (int)e;
     int rc = launch_kernel(moe_pairs_up_kernel<TA, TW, R, U>, dim3(T * top, (F + rows - 1) / rows), dim3(threads), smem_up, stream,
-                           (const TA*)x, (const TW*)w_up, ids, wts, (TA*)hid, h, E, F, top, kind, gated);
+                           (const TA*)x, (const TW*)w_up, ids, wts, (TA*)hid, h, E, F, top, kind, gated, limit);
     if (rc != 0) return rc;
     return launch_kernel(moe_pairs_down_kernel<TA, TW, R, U>, dim3(T, (h + rows - 1) / rows), dim3(threads), smem_down, stream,
                          (const TA*)hid, (const TW*)w_down, ids, out, h, E, F, top);
@@ -469,15 +482,15 @@ static int launch_pairs_as(const void* x, const void* w_up, const void* w_down, 
 
 template <typename TA, typename TW>
 static int launch_pairs(const void* x, const void* w_up, const void* w_down, const int* ids, const float* wts, void* hid, float* out,
-                        int T, int h, int E, int F, int top, int kind, int gated, cudaStream_t stream) {
+                        int T, int h, int E, int F, int top, int kind, int gated, float limit, cudaStream_t stream) {
     // fewer warps a block where a handful of tokens would leave SMs without one (the warps' work does not depend on it)
     const int threads = (int64_t)T * ((h + 31) / 32) < 2 * device_sm_count() ? 128 : 256;
     // the output rows of the smaller of the two products, four a warp: under 12 warps an SM the narrow form (measured at width
     // 2,048, four experts of 960 a token: one token 52 against 64 us, eight tokens 94 against 81 us)
     const int64_t quads = (int64_t)T * ((h < (int64_t)top * F ? h : top * F) / 4);
     if (quads < 12 * (int64_t)device_sm_count())
-        return launch_pairs_as<TA, TW, 1, 4>(x, w_up, w_down, ids, wts, hid, out, T, h, E, F, top, kind, gated, threads, stream);
-    return launch_pairs_as<TA, TW, 4, 1>(x, w_up, w_down, ids, wts, hid, out, T, h, E, F, top, kind, gated, threads, stream);
+        return launch_pairs_as<TA, TW, 1, 4>(x, w_up, w_down, ids, wts, hid, out, T, h, E, F, top, kind, gated, threads, limit, stream);
+    return launch_pairs_as<TA, TW, 4, 1>(x, w_up, w_down, ids, wts, hid, out, T, h, E, F, top, kind, gated, threads, limit, stream);
 }
 
 // Whether the pair kernels take these sizes: rows of whole 16-byte pieces, and a token's hidden rows within shared memory.
@@ -487,17 +500,17 @@ extern "C" int mie_moe_pairs_fit(int h, int F, int top) {
 
 // x [T, h] and hid [T * top, F] in the activation type (act_tag), w_up [E * F, h] and w_down [h, E * F] in w_tag, out [T, h] float32.
 extern "C" int mie_moe_pairs(const void* x, int act_tag, const void* w_up, const void* w_down, int w_tag, const int* ids, const float* wts,
-                             void* hid, float* out, int num_tokens, int h, int E, int F, int top, int kind, int gated,
+                             void* hid, float* out, int num_tokens, int h, int E, int F, int top, int kind, int gated, float limit,
                              cudaStream_t stream) {
     if (num_tokens <= 0) return 0;
-    if (E <= 0 || top <= 0 || kind < 0 || kind > 2 || !mie_moe_pairs_fit(h, F, top)) return MIE_ERR_BAD_ARG;
+    if (E <= 0 || top <= 0 || kind < 0 || kind > 3 || (kind == 3 && !gated) || !mie_moe_pairs_fit(h, F, top)) return MIE_ERR_BAD_ARG;
     if (((reinterpret_cast<uintptr_t>(w_up) | reinterpret_cast<uintptr_t>(w_down)) & 15) != 0) return MIE_ERR_BAD_ARG;
     if (act_tag == MIE_F32 && w_tag == MIE_F32)
-        return launch_pairs<float, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, stream);
+        return launch_pairs<float, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, limit, stream);
     if (act_tag == MIE_BF16 && w_tag == MIE_BF16)
-        return launch_pairs<bf16, bf16>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, stream);
+        return launch_pairs<bf16, bf16>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, limit, stream);
     if (act_tag == MIE_BF16 && w_tag == MIE_F32)
-        return launch_pairs<bf16, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, stream);
+        return launch_pairs<bf16, float>(x, w_up, w_down, ids, wts, hid, out, num_tokens, h, E, F, top, kind, gated, limit, stream);
     return MIE_ERR_BAD_ARG;
 }
 
@@ -669,7 +682,7 @@ extern "C" int mie_moe_combine(const void* rows, const int* place, float* out, i
 }
 
 static bool rule_ok(const RouteRule& rr, int E, int top) {
-    if (rr.mode != 0 && rr.mode != 1) return false;
+    if (rr.mode < 0 || rr.mode > 2) return false;
     if (rr.real < 0 || rr.real > E) return false;
     if (rr.mode == 1 && rr.groups > 1) {
         if (rr.groups > 64 || E % rr.groups || rr.keep < 1 || (rr.keep < rr.groups && top > rr.keep * (E / rr.groups))) return false;
@@ -768,7 +781,7 @@ extern "C" int mie_moe_dense_act(const void* up, const int* ids, const float* wt
 // expert and 0 for the others, with gu [T, E, 2F].  `per_row` = 1 for the rows form (E = 1, the weight by row).
 template <typename T>
 __global__ void moe_glu_kernel(const T* __restrict__ gu, const int* __restrict__ ids, const float* __restrict__ wts, T* __restrict__ act,
-                               int64_t total, int E, int F, int top, int kind, int per_row) {
+                               int64_t total, int E, int F, int top, int kind, int per_row, float limit) {
     pdl_enter();
     const int64_t EF = (int64_t)E * F;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -780,11 +793,11 @@ __global__ void moe_glu_kernel(const T* __restrict__ gu, const int* __restrict__
             for (int k = 0; k < top; ++k)
                 if (ids[t * top + k] == e) w = wts[t * top + k];
         const int64_t at = (t * E + e) * 2 * F + f;
-        act[idx] = from_f32<T>(w != 0.f ? w * expert_act(to_f32<T>(gu[at]), kind) * to_f32<T>(gu[at + F]) : 0.f);
+        act[idx] = from_f32<T>(w != 0.f ? gated_value(to_f32<T>(gu[at]), to_f32<T>(gu[at + F]), w, kind, limit) : 0.f);
     }
 }
 __global__ void moe_glu_bf16x8_kernel(const bf16* __restrict__ gu, const int* __restrict__ ids, const float* __restrict__ wts,
-                                      bf16* __restrict__ act, int64_t total8, int E, int F8, int top, int kind, int per_row) {
+                                      bf16* __restrict__ act, int64_t total8, int E, int F8, int top, int kind, int per_row, float limit) {
     pdl_enter();
     const int64_t EF8 = (int64_t)E * F8;
     for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (int64_t)gridDim.x * blockDim.x) {
@@ -805,7 +818,7 @@ __global__ void moe_glu_bf16x8_kernel(const bf16* __restrict__ gu, const int* __
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float2 a = __bfloat1622float2(hg[i]), b = __bfloat1622float2(hu[i]);
-                ho[i] = __floats2bfloat162_rn(w * expert_act(a.x, kind) * b.x, w * expert_act(a.y, kind) * b.y);
+                ho[i] = __floats2bfloat162_rn(gated_value(a.x, b.x, w, kind, limit), gated_value(a.y, b.y, w, kind, limit));
             }
         }
         *reinterpret_cast<uint4*>(act + idx * 8) = o;
@@ -814,18 +827,18 @@ __global__ void moe_glu_bf16x8_kernel(const bf16* __restrict__ gu, const int* __
 
 // gu [rows, E, 2F] -> act [rows, E, F]; per_row: E must be 1 and wts holds one weight a row (ids unused).
 extern "C" int mie_moe_glu(const void* gu, const int* ids, const float* wts, void* act, int tag, int rows, int E, int F, int top, int kind,
-                           int per_row, cudaStream_t stream) {
+                           int per_row, float limit, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (E <= 0 || F <= 0 || kind < 0 || kind > 2 || (per_row ? E != 1 : (top <= 0 || !ids))) return MIE_ERR_BAD_ARG;
+    if (E <= 0 || F <= 0 || kind < 0 || kind > 3 || (per_row ? E != 1 : (top <= 0 || !ids))) return MIE_ERR_BAD_ARG;
     const int64_t total = (int64_t)rows * E * F;
     if (tag == MIE_BF16 && F % 8 == 0 && ((reinterpret_cast<uintptr_t>(gu) | reinterpret_cast<uintptr_t>(act)) & 15) == 0)
         return launch_kernel(moe_glu_bf16x8_kernel, dim3(capped_blocks(total / 8, 256)), dim3(256), 0, stream, (const bf16*)gu, ids, wts,
-                             (bf16*)act, total / 8, E, F / 8, top, kind, per_row);
+                             (bf16*)act, total / 8, E, F / 8, top, kind, per_row, limit);
     if (tag == MIE_F32)
         return launch_kernel(moe_glu_kernel<float>, dim3(capped_blocks(total, 256)), dim3(256), 0, stream, (const float*)gu, ids, wts,
-                             (float*)act, total, E, F, top, kind, per_row);
+                             (float*)act, total, E, F, top, kind, per_row, limit);
     else if (tag == MIE_BF16)
         return launch_kernel(moe_glu_kernel<bf16>, dim3(capped_blocks(total, 256)), dim3(256), 0, stream, (const bf16*)gu, ids, wts,
-                             (bf16*)act, total, E, F, top, kind, per_row);
+                             (bf16*)act, total, E, F, top, kind, per_row, limit);
     return MIE_ERR_BAD_ARG;
 }

@@ -32,10 +32,13 @@
 #define RET_TT 16       // tokens staged at a time
 #define RET_L 64        // tokens per chunk
 
+// `act` 1: q and k pass silu first (a linear attention over activated projections).  `q_scale` multiplies q; `k_tok`
+// (optional, [T, H] float32) is one more factor on a token's key per head (a write gate folded into the key).
 template <typename T>
 __global__ void retention_prepare_kernel(const T* __restrict__ qkv, int64_t stride, const int* __restrict__ positions,
                                          const float* __restrict__ freq, float k_scale, float* __restrict__ qr,
-                                         float* __restrict__ kr, int H, int D, int rot) {
+                                         float* __restrict__ kr, int H, int D, int rot, int act, float q_scale,
+                                         const float* __restrict__ k_tok) {
     extern __shared__ float cs[];                 // cos [rot/2], sin [rot/2]
     pdl_enter();
     const int t = blockIdx.x, half = rot >> 1;
@@ -50,6 +53,7 @@ __global__ void retention_prepare_kernel(const T* __restrict__ qkv, int64_t stri
     for (int i = threadIdx.x; i < H * D; i += blockDim.x) {
         const int d = i % D;
         float qo = to_f32<T>(src[i]), ko = to_f32<T>(src[H * D + i]);
+        if (act) { qo = qo / (1.0f + expf(-qo)); ko = ko / (1.0f + expf(-ko)); }
         if (d < rot) {
             const int j = d < half ? d : d - half;
             const int pi = d < half ? i + half : i - half;
@@ -58,8 +62,8 @@ __global__ void retention_prepare_kernel(const T* __restrict__ qkv, int64_t stri
             qo = d < half ? qo * c - qp * sn : qo * c + qp * sn;
             ko = d < half ? ko * c - kp * sn : ko * c + kp * sn;
         }
-        qr[(int64_t)t * H * D + i] = qo;
-        kr[(int64_t)t * H * D + i] = ko * k_scale;
+        qr[(int64_t)t * H * D + i] = qo * q_scale;
+        kr[(int64_t)t * H * D + i] = ko * (k_tok ? k_scale * k_tok[(int64_t)t * H + i / D] : k_scale);
     }
 }
 
@@ -102,12 +106,17 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
                                        const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
                                        const float* __restrict__ decay, float* __restrict__ state,
                                        float* __restrict__ scratch, float* __restrict__ out, int num_rows, int H, int D, int Dv,
-                                       int CW, int slices) {
+                                       int CW, int slices, const float* __restrict__ tok_decay, float* __restrict__ chunk_decay,
+                                       int Dv_in, int v_act) {
+    // `tok_decay` (optional, [T, H]): the decay of every token instead of one per head; pass 0 then leaves the product of
+    // a chunk's decays in `chunk_decay` for the combine.  `Dv_in` < Dv: v has Dv_in columns a head and the state's column
+    // Dv_in is fed with ones (the sum of the keys under the same decays: a normalizer).  `v_act`: v passes silu.
     constexpr int DPAD = P * RET_DPT;        // key dimensions as the threads of a column hold them: D padded with zeros
     extern __shared__ float smem[];
     float* q_s = smem;                       // [RET_TT][DPAD]
     float* k_s = q_s + RET_TT * DPAD;        // [RET_TT][DPAD]
     float* v_s = k_s + RET_TT * DPAD;        // [RET_TT][CW]
+    float* a_s = v_s + RET_TT * CW;          // [RET_TT] the tokens' decays
     pdl_enter();
     int within, items, before0;
     const int r = find_chunk(row_q_len, num_rows, (int)blockIdx.y, PASS, within, items, before0);
@@ -117,7 +126,7 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
     const int t_lo = within * RET_L, t_hi = min(q_len, t_lo + RET_L);
     // a thread holds NC value columns, CW / NC apart (the key and query it reads from shared memory serve all of them)
     const int p = threadIdx.x % P, cl = threadIdx.x / P, cstep = CW / NC;
-    const float gamma = decay[h];
+    const float gamma = decay ? decay[h] : 1.f;
     const int64_t per_state = (int64_t)H * Dv * D;
     int c[NC];
     bool col_ok[NC];
@@ -154,12 +163,19 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
         for (int i = threadIdx.x; i < nt * CW; i += blockDim.x) {
             const int tt = i / CW, cc = i - tt * CW;
             const int col = slice * CW + cc;
-            v_s[i] = col < Dv ? to_f32<T>(v[(int64_t)(q_start + t0 + tt) * v_stride + h * Dv + col]) : 0.f;
+            float vv = 0.f;
+            if (col < Dv_in) {
+                vv = to_f32<T>(v[(int64_t)(q_start + t0 + tt) * v_stride + h * Dv_in + col]);
+                if (v_act) vv = vv / (1.0f + expf(-vv));
+            } else if (col < Dv) vv = 1.0f;
+            v_s[i] = vv;
         }
+        if (threadIdx.x < nt) a_s[threadIdx.x] = tok_decay ? tok_decay[(int64_t)(q_start + t0 + threadIdx.x) * H + h] : gamma;
         __syncthreads();
         float* o_ptr = out + (int64_t)(q_start + t0) * H * Dv + h * Dv;
         for (int tt = 0; tt < nt; ++tt) {
             float vv[NC], acc0[NC], acc1[NC];
+            const float gamma_t = a_s[tt];
 #pragma unroll
             for (int n = 0; n < NC; ++n) { vv[n] = v_mine[tt * CW + n * cstep]; acc0[n] = 0.f; acc1[n] = 0.f; }
             const float4* kt = k_mine + tt * (DPAD / 4);
@@ -171,10 +187,10 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
                 if (PASS) qq = qt[P * j4];
 #pragma unroll
                 for (int n = 0; n < NC; ++n) {
-                    S[n][4 * j4 + 0] = fmaf(gamma, S[n][4 * j4 + 0], kk.x * vv[n]);
-                    S[n][4 * j4 + 1] = fmaf(gamma, S[n][4 * j4 + 1], kk.y * vv[n]);
-                    S[n][4 * j4 + 2] = fmaf(gamma, S[n][4 * j4 + 2], kk.z * vv[n]);
-                    S[n][4 * j4 + 3] = fmaf(gamma, S[n][4 * j4 + 3], kk.w * vv[n]);
+                    S[n][4 * j4 + 0] = fmaf(gamma_t, S[n][4 * j4 + 0], kk.x * vv[n]);
+                    S[n][4 * j4 + 1] = fmaf(gamma_t, S[n][4 * j4 + 1], kk.y * vv[n]);
+                    S[n][4 * j4 + 2] = fmaf(gamma_t, S[n][4 * j4 + 2], kk.z * vv[n]);
+                    S[n][4 * j4 + 3] = fmaf(gamma_t, S[n][4 * j4 + 3], kk.w * vv[n]);
                     if (PASS) {
                         acc0[n] = fmaf(S[n][4 * j4 + 0], qq.x, acc0[n]);
                         acc1[n] = fmaf(S[n][4 * j4 + 1], qq.y, acc1[n]);
@@ -193,6 +209,11 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
                 }
             }
         }
+    }
+    if (PASS == 0 && tok_decay && slice == 0 && threadIdx.x == 0) {      // what this chunk does to the state it starts from
+        float prod = 1.f;
+        for (int t = t_lo; t < t_hi; ++t) prod *= tok_decay[(int64_t)(q_start + t) * H + h];
+        chunk_decay[(int64_t)(before0 + within + 1) * H + h] = prod;
     }
     float* to = PASS == 0 ? scratch + (int64_t)(before0 + within + 1) * per_state
                           : (within == items - 1 ? state + (int64_t)state_slots[r] * per_state : nullptr);
@@ -214,13 +235,14 @@ __global__ void retention_chunk_kernel(const float* __restrict__ qr, const float
 // row's chunks in order, eight loads ahead of the dependent multiply-adds.
 __global__ void retention_combine_kernel(const int* __restrict__ row_q_len, const int* __restrict__ state_slots,
                                          const float* __restrict__ decay, const float* __restrict__ state,
-                                         float* __restrict__ scratch, int num_rows, int H, int Dv, int D) {
+                                         float* __restrict__ scratch, int num_rows, int H, int Dv, int D,
+                                         const float* __restrict__ chunk_decay) {
     pdl_enter();
     const int64_t per_state = (int64_t)H * Dv * D;
     const int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= per_state) return;
     const int h = (int)(e / ((int64_t)Dv * D));
-    const float g = exp2f((float)RET_L * log2f(decay[h]));
+    const float g_head = chunk_decay ? 0.f : exp2f((float)RET_L * log2f(decay[h]));      // (decay may be null with token decays)
     int before0 = 0;
     for (int r = 0; r < num_rows; ++r) {
         const int items = (row_q_len[r] + RET_L - 1) / RET_L;
@@ -235,6 +257,7 @@ __global__ void retention_combine_kernel(const int* __restrict__ row_q_len, cons
 #pragma unroll
             for (int k = 0; k < 8; ++k)
                 if (j0 + k < items) {
+                    const float g = chunk_decay ? chunk_decay[(int64_t)(before0 + j0 + k) * H + h] : g_head;
                     cur = fmaf(g, cur, add[k]);
                     slot[(int64_t)(j0 + k) * per_state] = cur;
                 }
@@ -264,13 +287,20 @@ __global__ void head_rms_gate_kernel(const float* __restrict__ o, const T* __res
     }
 }
 
-extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, const int* positions, const int* row_q_start,
-                                  const int* row_q_len, const int* state_slots, const float* decay, const float* freq,
-                                  float k_scale, float* state, float* qr, float* kr, float* scratch, long long scratch_chunks,
-                                  float* out, int num_tokens, int num_rows, int max_q_len, int H, int D, int Dv, int rot,
-                                  cudaStream_t stream) {
+// The general entry.  `rows_in` holds [ q: H x D | k: H x D | v: H x Dv_in | ... ] per token.  `act`: q, k and v pass silu
+// (no rotation then).  `tok_decay` / `k_tok` (optional, float32 [T, H]): a decay and a factor on the key per token and head,
+// in place of `decay` [H].  `ones`: the state and the output have one more column per head, Dv_in + 1 in all, fed with ones.
+// state [slots, H, Dv, D], out [T, H, Dv] with Dv = Dv_in + ones; `chunk_decay`: scratch of (scratch_chunks + 1) * H floats.
+extern "C" int mie_decay_scan(const void* qkv, int tag, long long stride, const int* positions, const int* row_q_start,
+                              const int* row_q_len, const int* state_slots, const float* decay, const float* freq,
+                              float q_scale, float k_scale, const float* tok_decay, const float* k_tok, int act, int ones,
+                              float* state, float* qr, float* kr, float* scratch, long long scratch_chunks, float* chunk_decay,
+                              float* out, int num_tokens, int num_rows, int max_q_len, int H, int D, int Dv_in, int rot,
+                              cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
-    if (H <= 0 || D <= 0 || Dv <= 0 || rot < 0 || rot > D || (rot & 1)) return MIE_ERR_BAD_ARG;
+    if (H <= 0 || D <= 0 || Dv_in <= 0 || rot < 0 || rot > D || (rot & 1) || (act && rot) || (!decay && !tok_decay) || ones < 0 || ones > 1)
+        return MIE_ERR_BAD_ARG;
+    const int Dv = Dv_in + ones;
     int P = 1;
     while (P * RET_DPT < D) P <<= 1;
     if (P > 32) return MIE_ERR_TOO_LARGE;                      // key dimensions beyond 32 x RET_DPT
@@ -284,9 +314,10 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
         c.NC = nc;
         c.CW = nc * (256 / P);                                 // columns a block
         if (c.CW > Dv) c.CW = Dv;
+        if (nc == 2 && (c.CW & 1)) c.CW += 1;                  // two columns a thread: an even count (the odd one out is masked)
         c.slices = (Dv + c.CW - 1) / c.CW;
         c.threads = (c.CW / nc * P + 31) / 32 * 32;
-        c.smem = (size_t)RET_TT * (2 * P * RET_DPT + c.CW) * sizeof(float);
+        c.smem = (size_t)RET_TT * (2 * P * RET_DPT + c.CW + 1) * sizeof(float);
         return c;
     };
     const Cut cut0 = cut(Dv >= 2 * (256 / P) ? 2 : 1), cut1 = cut(1);
@@ -294,6 +325,8 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
     // (such a row has more than RET_L tokens): two per RET_L tokens
     const int chunks1 = num_rows + num_tokens / RET_L, chunks0 = max_q_len > RET_L ? 2 * (num_tokens / RET_L) : 0;
     if (chunks0 > scratch_chunks) return MIE_ERR_BAD_ARG;
+    if (chunks0 > 0 && tok_decay && !chunk_decay) return MIE_ERR_BAD_ARG;
+    float* cdec = tok_decay ? chunk_decay : nullptr;
     const int prep_threads = H * D >= 1024 ? 256 : 128;
     int rc;
 #define RET_PASS(T, PASS, PP, ny)                                                                                             \
@@ -301,19 +334,19 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
 #define RET_PASS_N(T, PASS, PP, NN, ny, CUT)                                                                                  \
     launch_kernel(retention_chunk_kernel<T, PASS, PP, NN>, dim3(H * CUT.slices, ny), dim3(CUT.threads), CUT.smem, stream, qr, \
                   kr, (const T*)qkv + 2 * H * D, (int64_t)stride, row_q_start, row_q_len, state_slots, decay, state, scratch, \
-                  out, num_rows, H, D, Dv, CUT.CW, CUT.slices)
+                  out, num_rows, H, D, Dv, CUT.CW, CUT.slices, tok_decay, cdec, Dv_in, act)
 #define RET_PASS_P(T, PASS, ny)                                                                                               \
     (P == 1 ? RET_PASS(T, PASS, 1, ny) : P == 2 ? RET_PASS(T, PASS, 2, ny) : P == 4 ? RET_PASS(T, PASS, 4, ny)                \
      : P == 8 ? RET_PASS(T, PASS, 8, ny) : P == 16 ? RET_PASS(T, PASS, 16, ny) : RET_PASS(T, PASS, 32, ny))
 #define RET_LAUNCH(T)                                                                                                         \
     rc = launch_kernel(retention_prepare_kernel<T>, dim3(num_tokens), dim3(prep_threads), (size_t)rot * sizeof(float), stream, \
-                       (const T*)qkv, (int64_t)stride, positions, freq, k_scale, qr, kr, H, D, rot);                          \
+                       (const T*)qkv, (int64_t)stride, positions, freq, k_scale, qr, kr, H, D, rot, act, q_scale, k_tok);     \
     if (rc) return rc;                                                                                                        \
     if (chunks0 > 0) {                                                                                                        \
         rc = RET_PASS_P(T, 0, chunks0);                                                                                       \
         if (rc) return rc;                                                                                                    \
         rc = launch_kernel(retention_combine_kernel, dim3((unsigned)(((int64_t)H * Dv * D + 255) / 256)), dim3(256), 0, stream, \
-                           row_q_len, state_slots, decay, (const float*)state, scratch, num_rows, H, Dv, D);                  \
+                           row_q_len, state_slots, decay, (const float*)state, scratch, num_rows, H, Dv, D, (const float*)cdec); \
         if (rc) return rc;                                                                                                    \
     }                                                                                                                         \
     return RET_PASS_P(T, 1, chunks1);
@@ -324,6 +357,16 @@ extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, co
 #undef RET_PASS
 #undef RET_PASS_N
     return MIE_ERR_BAD_ARG;
+}
+
+extern "C" int mie_retention_scan(const void* qkv, int tag, long long stride, const int* positions, const int* row_q_start,
+                                  const int* row_q_len, const int* state_slots, const float* decay, const float* freq,
+                                  float k_scale, float* state, float* qr, float* kr, float* scratch, long long scratch_chunks,
+                                  float* out, int num_tokens, int num_rows, int max_q_len, int H, int D, int Dv, int rot,
+                                  cudaStream_t stream) {
+    return mie_decay_scan(qkv, tag, stride, positions, row_q_start, row_q_len, state_slots, decay, freq, 1.0f, k_scale, nullptr, nullptr,
+                          0, 0, state, qr, kr, scratch, scratch_chunks, nullptr, out, num_tokens, num_rows, max_q_len, H, D, Dv, rot,
+                          stream);
 }
 
 extern "C" int mie_retention_chunk_tokens() { return RET_L; }
@@ -341,5 +384,98 @@ extern "C" int mie_head_rms_gate(const float* o, const void* g, int tag, long lo
     else if (tag == MIE_BF16)
         return launch_kernel(head_rms_gate_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, o, (const bf16*)g,
                              (int64_t)g_stride, (bf16*)out, num_tokens, H, Dv, eps);
+    return MIE_ERR_BAD_ARG;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Exponential gates with a running maximum, for a matrix memory whose decay and write strength change with the token
+// (the scan above then runs with `tok_decay` = keep and `k_tok` = write):
+//   i_t = cap tanh((zi_t + bi) / cap)          f_t = logsigmoid(cap tanh((zf_t + bf) / cap))        (cap <= 0: no cap)
+//   m_t = max(f_t + m_{t-1}, i_t)              keep_t = exp(f_t + m_{t-1} - m_t)      write_t = exp(i_t - m_t)
+// z [T, 2H] float32 holds [zi: H | zf: H] per token; m_state [slots, H] carries m between steps (0 for a fresh request).
+// One thread per (row, head) walks the row's tokens in order: the chain is a handful of scalar operations a token.
+__global__ void gate_scan_kernel(const float* __restrict__ z, const float* __restrict__ bi, const float* __restrict__ bf, float cap,
+                                 const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
+                                 const int* __restrict__ state_slots, float* __restrict__ m_state, float* __restrict__ keep,
+                                 float* __restrict__ write, float* __restrict__ m_out, int num_rows, int H) {
+    pdl_enter();
+    const int item = blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= num_rows * H) return;
+    const int r = item / H, h = item - r * H;
+    const int start = row_q_start[r], len = row_q_len[r];
+    float* ms = m_state + (int64_t)state_slots[r] * H + h;
+    float m = *ms;
+    const float b_i = bi ? bi[h] : 0.f, b_f = bf ? bf[h] : 0.f, inv = cap > 0.f ? 1.0f / cap : 0.f;
+    for (int t = start; t < start + len; ++t) {
+        float zi = z[(int64_t)t * 2 * H + h] + b_i, zf = z[(int64_t)t * 2 * H + H + h] + b_f;
+        if (cap > 0.f) { zi = cap * tanhf(zi * inv); zf = cap * tanhf(zf * inv); }
+        const float f = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));           // log sigmoid
+        const float m_new = fmaxf(f + m, zi);
+        keep[(int64_t)t * H + h] = expf(f + m - m_new);
+        write[(int64_t)t * H + h] = expf(zi - m_new);
+        m_out[(int64_t)t * H + h] = m_new;
+        m = m_new;
+    }
+    *ms = m;
+}
+
+extern "C" int mie_gate_scan(const float* z, const float* bi, const float* bf, float cap, const int* row_q_start, const int* row_q_len,
+                             const int* state_slots, float* m_state, float* keep, float* write, float* m_out, int num_rows, int H,
+                             cudaStream_t stream) {
+    if (num_rows <= 0) return 0;
+    if (H <= 0) return MIE_ERR_BAD_ARG;
+    const int items = num_rows * H, threads = 64;
+    return launch_kernel(gate_scan_kernel, dim3((items + threads - 1) / threads), dim3(threads), 0, stream, z, bi, bf, cap, row_q_start,
+                         row_q_len, state_slots, m_state, keep, write, m_out, num_rows, H);
+}
+
+// What follows a linear-attention scan in several mixers, as one kernel: o [T, groups, stride] float32 holds `size` outputs per
+// group (stride >= size; with `normalizer` the entry behind them is n . q and `m` [T, groups] the running maximum: the group is
+// first divided by max(|n . q|, exp(-m)) + 1e-6); each group is divided by its root mean square (eps inside the root),
+// multiplied by a weight (`w_len` entries, indexed by the output's place in the row modulo w_len: one weight per head, or one
+// for the whole row; null: none) and by a gate read from `gate` (sigmoid, or silu with `gate_silu`).  groups = 1 norms the
+// whole row at once.  A warp per (token, group).
+template <typename T>
+__global__ void group_norm_gate_kernel(const float* __restrict__ o, int stride, const float* __restrict__ m, const float* __restrict__ w,
+                                       int w_len, const T* __restrict__ gate, int64_t g_stride, T* __restrict__ out, int num_tokens,
+                                       int groups, int size, float eps, int normalizer, int gate_silu) {
+    pdl_enter();
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)num_tokens * groups) return;
+    const int64_t t = item / groups;
+    const int g = (int)(item - t * groups);
+    const float* src = o + item * stride;
+    float scale = 1.f;
+    if (normalizer) scale = 1.0f / (fmaxf(fabsf(src[size]), expf(-m[item])) + 1e-6f);
+    float ss = 0.f;
+    for (int i = lane; i < size; i += 32) { const float v = src[i] * scale; ss += v * v; }
+    const float s = scale / sqrtf(warp_sum(ss) / (float)size + eps);
+    const T* gt = gate ? gate + t * g_stride + (int64_t)g * size : nullptr;
+    for (int i = lane; i < size; i += 32) {
+        float v = src[i] * s;
+        if (w) v *= w[(g * size + i) % w_len];
+        if (gt) {
+            const float zz = to_f32<T>(gt[i]);
+            v *= gate_silu ? zz / (1.0f + expf(-zz)) : 1.0f / (1.0f + expf(-zz));
+        }
+        out[(t * groups + g) * size + i] = from_f32<T>(v);
+    }
+}
+
+extern "C" int mie_group_norm_gate(const float* o, int stride, const float* m, const float* w, int w_len, const void* gate, int tag,
+                                   long long g_stride, void* out, int num_tokens, int groups, int size, float eps, int normalizer,
+                                   int gate_silu, cudaStream_t stream) {
+    if (num_tokens <= 0) return 0;
+    if (groups <= 0 || size <= 0 || stride < size + (normalizer ? 1 : 0) || (w && w_len <= 0) || (normalizer && !m)) return MIE_ERR_BAD_ARG;
+    const int warps = 4;
+    const int64_t items = (int64_t)num_tokens * groups;
+    const int blocks = (int)((items + warps - 1) / warps);
+    if (tag == MIE_F32)
+        return launch_kernel(group_norm_gate_kernel<float>, dim3(blocks), dim3(warps * 32), 0, stream, o, stride, m, w, w_len,
+                             (const float*)gate, (int64_t)g_stride, (float*)out, num_tokens, groups, size, eps, normalizer, gate_silu);
+    else if (tag == MIE_BF16)
+        return launch_kernel(group_norm_gate_kernel<bf16>, dim3(blocks), dim3(warps * 32), 0, stream, o, stride, m, w, w_len,
+                             (const bf16*)gate, (int64_t)g_stride, (bf16*)out, num_tokens, groups, size, eps, normalizer, gate_silu);
     return MIE_ERR_BAD_ARG;
 }

@@ -57,11 +57,13 @@ def rotates_in_decode(dtype, head_dim: int, ctx) -> bool:
             and decode_only(ctx))
 
 
-def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, window, rope=None, q_stride=None):
+def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, window, rope=None, q_stride=None, mods=None):
     """``rope`` = (cos, sin): ``qkv`` is unrotated and the cache rows of the new tokens are unwritten; only
     where ``rotates_in_decode`` holds.  ``window``: None or 0 all earlier keys, w > 0 the last w positions, w < 0 the
     keys of the query's own block of -w positions.  ``q_stride``: elements between the token rows of ``qkv`` (by
-    default rows of a fused q|k|v projection)."""
+    default rows of a fused q|k|v projection).  ``mods`` (``ops.ScoreMods``): a cap on the scores, a bias by distance, a sink in
+    the softmax; the CUDA-core, decode and mma.sync kernels apply them, so portions with head sizes 64 and 128 go to the
+    mma.sync kernel when a layer has any."""
     if q_stride is None:
         q_stride = (num_heads + 2 * num_kv_heads) * head_dim
     args = (qkv, q_stride, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_q_start, ctx.row_q_len,
@@ -71,6 +73,8 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
     # the keys a single new token can reach, for the decode kernel's plan: a window or a block of positions bounds them
     reach = ctx.max_ctx_len if window == 0 else min(ctx.max_ctx_len, abs(window) + 64)
     if rope is not None:
+        if mods is not None:
+            raise ValueError("rotation inside attention and score modifiers do not go together")
         if not rotates_in_decode(qkv.dtype, head_dim, ctx):
             raise ValueError("rotation inside attention serves steps of decoding rows only (bfloat16, head sizes "
                              "in steps of 32 up to 128)")
@@ -78,7 +82,7 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
                                     max_ctx=ctx.max_ctx_len, rope=rope)
     if not fast:
         return ops.paged_attention(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size,
-                                   scale, window)
+                                   scale, window, mods=mods)
     kinds = _row_kinds(ctx)
     has_decode = kinds is None or kinds[0] > 0
     has_prefill = kinds is None or kinds[1] > 0
@@ -89,13 +93,13 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
         has_decode, min_q_len = False, 1
     if has_decode:
         ops.decode_attention(*args, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
-                             max_ctx=reach)
+                             max_ctx=reach, mods=mods)
     if has_prefill:
         # tcgen05 (S and O in tensor memory) for the head sizes it is written for, mma.sync otherwise
-        tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05"
+        tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05" and mods is None
         fn = ops.prefill_attention_tc if tc else ops.prefill_attention
         # the rows that are portions, and their tokens: the launch is laid out for those, not for every decoding row
         work = None if kinds is None else (kinds[1], kinds[2])
         fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
-           min_q_len=min_q_len, work=work)
+           min_q_len=min_q_len, work=work, **({} if tc else {"mods": mods}))
     return out

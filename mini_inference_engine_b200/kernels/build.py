@@ -36,7 +36,7 @@ SOURCES = ("embedding", "norm", "rope_cache", "attention_simt", "attention_decod
            "attention_prefill_tc",
            "activation", "gemm_simt", "gemm_tcgen05", "gemm_chain", "gemm_pair_tc",
            "sampling", "norm_group", "qk_norm_rope", "retention", "linear_recurrence",
-           "hyper_norm", "latent_kv", "diff_attention", "delta_rule", "moe", "stream_update")
+           "hyper_norm", "latent_kv", "diff_attention", "delta_rule", "moe", "stream_update", "layer_norm")
 
 _libs: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -254,6 +254,54 @@ def add_rmsnorm(delta, res: torch.Tensor, weight: torch.Tensor, eps: float, out:
 
 # --------------------------------------------------------------------------- rope + cache write
 
+def _delta_args(deltas, coefs, shape):
+    """Up to two addends with their coefficients as kernel arguments (pointer, tag, coefficient each)."""
+    _need(len(deltas) <= 2 and len(coefs) == len(deltas), "one or two addends, a coefficient each")
+    out = []
+    for d, c in zip(deltas, coefs):
+        _need(d.is_contiguous() and tuple(d.shape) == tuple(shape) and d.dtype in (torch.float32, torch.bfloat16), "an addend must be contiguous, of the stream's shape, float32 or bfloat16")
+        out += [_ptr(d), tag(d), ctypes.c_float(float(c))]
+    for _ in range(2 - len(deltas)):
+        out += [None, 0, ctypes.c_float(0.0)]
+    return out
+
+
+def add_layernorm(res: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, *, deltas=(), coefs=(), rows=None, center: bool = True,
+                  res_coef: float = 1.0) -> torch.Tensor:
+    """res <- res_coef res + sum_k coefs[k] deltas[k] (in place; up to two addends, float32 or bfloat16), then
+    out = (res - mean) / sqrt(var + eps) * weight per row (``center`` False: the mean is taken as 0, an RMS norm).  With ``rows``
+    output row b comes from row rows[b] and the stream is left as it is."""
+    T, n = res.shape
+    _need(res.dtype == torch.float32 and res.is_contiguous(), "the stream must be contiguous float32")
+    _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == n, "float32 norm weight [n]")
+    n_out = T
+    if rows is not None:
+        _i32(rows, "rows")
+        n_out = rows.numel()
+    _need(out.is_contiguous() and tuple(out.shape) == (n_out, n), "norm output shape")
+    _check(load("layer_norm").mie_add_layernorm(_ptr(res), ctypes.c_float(res_coef), *_delta_args(deltas, coefs, res.shape), _ptr(weight), _ptr(out),
+                                                tag(out), _ptr(rows), n_out, n, ctypes.c_float(eps), int(center), T, _stream()), "add_layernorm")
+    return out
+
+
+def stream_join(res: torch.Tensor, extra: torch.Tensor, out: torch.Tensor, *, deltas=(), coefs=(), res_coef: float = 1.0) -> torch.Tensor:
+    """out[t] = [res_coef res[t] + sum_k coefs[k] deltas[k][t] | extra[t]] in out's type (the stream is not written)."""
+    T, n = res.shape
+    _need(res.dtype == torch.float32 and res.is_contiguous() and extra.dtype == torch.float32 and extra.is_contiguous() and extra.shape == res.shape,
+          "the stream and the second stream must be contiguous float32 of one shape")
+    _need(out.is_contiguous() and tuple(out.shape) == (T, 2 * n), "joined rows are [T, 2 n]")
+    _check(load("layer_norm").mie_stream_join(_ptr(res), ctypes.c_float(res_coef), *_delta_args(deltas, coefs, res.shape), _ptr(extra), _ptr(out),
+                                              tag(out), T, n, _stream()), "stream_join")
+    return out
+
+
+def tanh_cap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap tanh(x / cap) in place (float32)."""
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "tanh_cap works on contiguous float32")
+    _check(load("layer_norm").mie_tanh_cap(_ptr(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), _stream()), "tanh_cap")
+    return x
+
+
 def rope_tables(inv_freq: torch.Tensor, max_pos: int):
     """cos, sin [max_pos, rotary_dim/2] float32 of p * inv_freq[j]."""
     _need(inv_freq.dtype == torch.float32 and inv_freq.is_contiguous(), "inv_freq must be float32")
@@ -287,10 +335,31 @@ def rope_cache_write(qkv: torch.Tensor, positions, slots, cos, sin, k_cache, v_c
 
 # --------------------------------------------------------------------------- attention
 
+class ScoreMods:
+    """What an attention kernel does to a score between the scaled product and the softmax.  ``softcap`` c > 0: s <- c tanh(s / c).
+    ``dist_bias`` float32 [L, heads]: the query at position p adds row min(p - j, L - 1) to the score of key j (after the cap).
+    ``sink`` float32 [heads]: exp(sink[head]) is one more term of the softmax's denominator, with no key and no value."""
+
+    def __init__(self, softcap: float = 0.0, sink=None, dist_bias=None):
+        self.softcap, self.sink, self.dist_bias = float(softcap or 0.0), sink, dist_bias
+
+    def args(self, num_heads: int):
+        if self.sink is not None:
+            _need(self.sink.dtype == torch.float32 and self.sink.is_contiguous() and self.sink.numel() == num_heads, "one float32 sink per head")
+        if self.dist_bias is not None:
+            _need(self.dist_bias.dtype == torch.float32 and self.dist_bias.is_contiguous() and self.dist_bias.dim() == 2
+                  and self.dist_bias.shape[1] == num_heads and self.dist_bias.shape[0] >= 1, "distance bias must be float32 [L, heads]")
+        return (ctypes.c_float(self.softcap), _ptr(self.sink), _ptr(self.dist_bias),
+                int(self.dist_bias.shape[0]) if self.dist_bias is not None else 0)
+
+
+_NO_MODS = ScoreMods()
+
+
 def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                     row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                     head_dim: int, page_size: int, scale: float, window: int | None = None,
-                    min_q_len: int = 1) -> torch.Tensor:
+                    min_q_len: int = 1, mods: ScoreMods | None = None) -> torch.Tensor:
     """Causal attention of every new token over its request's pages (CUDA-core kernel, float32 or
     bfloat16).  ``q`` holds [H, D] at the start of each token row of ``q_stride`` elements.  Rows
     with fewer than ``min_q_len`` new tokens are left alone."""
@@ -310,7 +379,8 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
                                    _ptr(row_ctx_len), rows, num_tokens, _ptr(out), tag(q), num_heads,
                                    num_kv_heads, head_dim, page_size, ctypes.c_float(scale),
                                    int(window or 0), int(min_q_len), ctypes.c_longlong(k_cache.shape[0]),
-                                   int(out.dtype == torch.float32 and q.dtype != torch.float32), _stream()),
+                                   int(out.dtype == torch.float32 and q.dtype != torch.float32), *(mods or _NO_MODS).args(num_heads),
+                                   _stream()),
            "paged_attention")
     return out
 
@@ -318,7 +388,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tabl
 def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                       row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                       head_dim: int, page_size: int, scale: float, window: int | None = None,
-                      min_q_len: int = 2, work=None) -> torch.Tensor:
+                      min_q_len: int = 2, work=None, mods: ScoreMods | None = None) -> torch.Tensor:
     """Causal attention of prompt portions over their request's pages (bfloat16, tensor cores).
     Rows with fewer than ``min_q_len`` new tokens are left alone.  ``work`` = (rows, tokens): how many rows have
     ``min_q_len`` tokens or more and their tokens in sum, where the caller knows -- the launch then has blocks for the
@@ -338,7 +408,7 @@ def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_ta
                                      _ptr(row_ctx_len), row_q_len.numel(), num_tokens, _ptr(out), num_heads,
                                      num_kv_heads, head_dim, page_size, ctypes.c_float(scale), int(window or 0),
                                      int(min_q_len), ctypes.c_longlong(k_cache.shape[0]), *_work_args(work),
-                                     int(out.dtype == torch.float32), _stream()),
+                                     int(out.dtype == torch.float32), *(mods or _NO_MODS).args(num_heads), _stream()),
            "prefill_attention")
     return out
 
@@ -515,7 +585,7 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                      row_ctx_len, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                      page_size: int, scale: float, window: int | None = None, max_ctx: int = 0,
                      splits: int | None = None, merge: str | None = None, stages: int | None = None,
-                     tma: bool | None = None, min_part_tiles: int = 0, rope=None) -> torch.Tensor:
+                     tma: bool | None = None, min_part_tiles: int = 0, rope=None, mods: ScoreMods | None = None) -> torch.Tensor:
     """Attention of rows with exactly one new token (bfloat16, tensor cores, context split across
     blocks and merged in the same launch).  Rows with more new tokens are skipped.  ``merge`` =
     "cluster": 1, 2, 4 or 8 splits merged through distributed shared memory; "scratch": any number of
@@ -576,7 +646,7 @@ def decode_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tab
                                     ctypes.c_int64(k_cache.shape[0] if tma else 0), ctypes.c_int64(k_cache.shape[0]),
                                     int(min_part_tiles if merge == "scratch" else 0),
                                     _ptr(cos), _ptr(sin), int(cos.shape[0]) if cos is not None else 0,
-                                    int(out.dtype == torch.float32), _stream()),
+                                    int(out.dtype == torch.float32), *(mods or _NO_MODS).args(num_heads), _stream()),
            "decode_attention")
     return out
 
@@ -685,10 +755,12 @@ def stream_norm(res: torch.Tensor, weight: torch.Tensor, groups: int, eps: float
 def qk_norm_rope(qkv: torch.Tensor, positions, slots, freq: torch.Tensor, q_out: torch.Tensor, k_cache, v_cache, *,
                  num_heads: int, num_kv_heads: int, dim: int, vdim: int, rot: int, page_size: int, eps: float = 0.0,
                  q_weight=None, k_weight=None, temp=None, q_scale: float = 1.0, k_scale: float = 1.0,
-                 write_cache: bool = True) -> torch.Tensor:
+                 write_cache: bool = True, head_norm: bool = False, interleaved: bool = False, pos_temp=None) -> torch.Tensor:
     """From the fused projection rows [q: H x dim | k: G x dim | v: G x vdim | ...]: q and k optionally RMS-normed over
-    their whole projection, rotated by position x ``freq`` over their first ``rot`` dims, q scaled per head, q written to
-    ``q_out`` [T, H, DP] and k, v to their cache slots (pages [page, G, page_size, DP], tails zero)."""
+    their whole projection (``head_norm``: per head, with ``dim`` weights shared by the heads), rotated by position x ``freq``
+    over their first ``rot`` dims (pairs (i, i + rot/2), or (2i, 2i + 1) with ``interleaved``), q scaled per head and, with
+    ``pos_temp`` = (coef, every), by 1 + coef ln(floor((position + 1) / every) + 1); q written to ``q_out`` [T, H, DP] and k, v
+    to their cache slots (pages [page, G, page_size, DP], tails zero)."""
     T = qkv.shape[0]
     DP = q_out.shape[-1]
     _need(qkv.dim() == 2 and qkv.stride(1) == 1
@@ -702,9 +774,10 @@ def qk_norm_rope(qkv: torch.Tensor, positions, slots, freq: torch.Tensor, q_out:
     ws = [w for w in (q_weight, k_weight, temp) if w is not None]
     _need(len({w.dtype for w in ws}) <= 1 and all(w.is_contiguous() for w in ws), "norm weights and temperatures must share a type")
     if q_weight is not None:
-        _need(q_weight.numel() == num_heads * dim, "q norm weight size")
+        _need(q_weight.numel() == (dim if head_norm else num_heads * dim), "q norm weight size")
     if k_weight is not None:
-        _need(k_weight.numel() == num_kv_heads * dim, "k norm weight size")
+        _need(k_weight.numel() == (dim if head_norm else num_kv_heads * dim), "k norm weight size")
+    coef, every = (float(pos_temp[0]), int(pos_temp[1])) if pos_temp else (0.0, 0)
     if temp is not None:
         _need(temp.numel() == num_heads, "one temperature per head")
     lib = load("qk_norm_rope")
@@ -712,7 +785,7 @@ def qk_norm_rope(qkv: torch.Tensor, positions, slots, freq: torch.Tensor, q_out:
                                 _ptr(q_weight), _ptr(k_weight), _ptr(temp), tag(ws[0]) if ws else 0, ctypes.c_float(eps),
                                 ctypes.c_float(q_scale), ctypes.c_float(k_scale), _ptr(q_out), _ptr(k_cache), _ptr(v_cache), T,
                                 num_heads, num_kv_heads, dim, vdim, DP, rot, page_size, ctypes.c_longlong(k_cache.shape[0]),
-                                int(write_cache), _stream()), "qk_norm_rope")
+                                int(write_cache), int(head_norm), int(interleaved), ctypes.c_float(coef), every, _stream()), "qk_norm_rope")
     return q_out
 
 
@@ -743,6 +816,89 @@ def retention_scan(qkv: torch.Tensor, positions, row_q_start, row_q_len, state_s
                                   _ptr(row_q_len), _ptr(state_slots), _ptr(decay), _ptr(freq), ctypes.c_float(k_scale),
                                   _ptr(state), _ptr(qr[0]), _ptr(qr[1]), _ptr(scratch), ctypes.c_longlong(chunks), _ptr(out), T,
                                   row_q_len.numel(), int(max_q_len), num_heads, dim, vdim, rot, _stream()), "retention_scan")
+    return out
+
+
+def decay_scan(rows_in: torch.Tensor, positions, row_q_start, row_q_len, state_slots, state, out, *, num_heads: int, dim: int, vdim: int,
+               max_q_len: int, decay=None, tok_decay=None, k_tok=None, act: bool = False, ones: bool = False, q_scale: float = 1.0,
+               k_scale: float = 1.0, freq=None, rot: int = 0) -> torch.Tensor:
+    """The general form of ``retention_scan``: S <- a S + k v^T, o = S^T q per head with a = ``decay`` [H] or, per token,
+    ``tok_decay`` [T, H]; ``k_tok`` [T, H] is one more factor on a token's key; ``act``: q, k and v pass silu (no rotation
+    then); ``ones``: the state and the output have a column more per head, fed with ones instead of a value (the decayed sum
+    of the keys).  ``rows_in`` rows hold [q: H x dim | k: H x dim | v: H x vdim | ...]; state [slots, H, vdim + ones, dim] and
+    out [T, H * (vdim + ones)] float32."""
+    T = rows_in.shape[0]
+    dv = vdim + int(ones)
+    _need(rows_in.dim() == 2 and rows_in.stride(1) == 1 and rows_in.shape[1] >= num_heads * (2 * dim + vdim), "rows must hold q, k and v")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (num_heads, dv, dim),
+          "state must be float32 [slots, H, vdim (+ 1), dim]")
+    _need(out.dtype == torch.float32 and out.is_contiguous() and out.shape == (T, num_heads * dv), "out must be float32 [T, H * (vdim (+ 1))]")
+    _need((decay is None) != (tok_decay is None), "a decay per head or per token and head, not both")
+    if decay is not None:
+        _need(decay.dtype == torch.float32 and decay.numel() == num_heads, "one float32 decay per head")
+    for t_, n in ((tok_decay, "tok_decay"), (k_tok, "k_tok")):
+        if t_ is not None:
+            _need(t_.dtype == torch.float32 and t_.is_contiguous() and t_.shape == (T, num_heads), f"{n} must be float32 [T, H]")
+    if freq is None:
+        freq = torch.empty(0, dtype=torch.float32, device=rows_in.device)
+    _need(freq.dtype == torch.float32 and freq.numel() * 2 == rot and not (act and rot), "one float32 frequency per rotated pair; no rotation of activated q, k")
+    for t_, n in ((positions, "positions"), (row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (state_slots, "state_slots")):
+        _i32(t_, n)
+    _need(positions.numel() == T, "one position per token")
+    lib = load("retention")
+    chunk = lib.mie_retention_chunk_tokens()
+    chunks = 2 * (T // chunk) if max_q_len > chunk else 0
+    scratch = _workspace(rows_in.device, "retention_chunks", chunks * num_heads * dv * dim, torch.float32) if chunks else None
+    cdec = _workspace(rows_in.device, "retention_chunk_decay", (chunks + 1) * num_heads, torch.float32) if chunks and tok_decay is not None else None
+    qr = torch.empty(2, T, num_heads * dim, dtype=torch.float32, device=rows_in.device)
+    _check(lib.mie_decay_scan(_ptr(rows_in), tag(rows_in), ctypes.c_longlong(rows_in.stride(0)), _ptr(positions), _ptr(row_q_start),
+                              _ptr(row_q_len), _ptr(state_slots), _ptr(decay), _ptr(freq), ctypes.c_float(q_scale), ctypes.c_float(k_scale),
+                              _ptr(tok_decay), _ptr(k_tok), int(act), int(ones), _ptr(state), _ptr(qr[0]), _ptr(qr[1]), _ptr(scratch),
+                              ctypes.c_longlong(chunks), _ptr(cdec), _ptr(out), T, row_q_len.numel(), int(max_q_len), num_heads, dim,
+                              vdim, rot, _stream()), "decay_scan")
+    return out
+
+
+def gate_scan(z: torch.Tensor, bias_i, bias_f, cap: float, row_q_start, row_q_len, state_slots, m_state: torch.Tensor, num_heads: int):
+    """Exponential gates with a running maximum, token by token per row and head: from z [T, 2H] float32 = [input | forget]
+    pre-activations, i = cap tanh((zi + bias_i) / cap), f = logsigmoid(cap tanh((zf + bias_f) / cap)) (``cap`` 0: no cap),
+    m_t = max(f + m_{t-1}, i), keep = exp(f + m_{t-1} - m_t), write = exp(i - m_t).  ``m_state`` [slots, H] float32 carries m.
+    Returns (keep, write, m), float32 [T, H] each."""
+    T = z.shape[0]
+    _need(z.dtype == torch.float32 and z.is_contiguous() and z.shape == (T, 2 * num_heads), "gate pre-activations must be float32 [T, 2H]")
+    _need(m_state.dtype == torch.float32 and m_state.is_contiguous() and tuple(m_state.shape[1:]) == (num_heads,), "m state must be float32 [slots, H]")
+    for b in (bias_i, bias_f):
+        if b is not None:
+            _need(b.dtype == torch.float32 and b.is_contiguous() and b.numel() == num_heads, "one float32 gate bias per head")
+    for t_, n in ((row_q_start, "row_q_start"), (row_q_len, "row_q_len"), (state_slots, "state_slots")):
+        _i32(t_, n)
+    keep, write, m = (torch.empty(T, num_heads, dtype=torch.float32, device=z.device) for _ in range(3))
+    _check(load("retention").mie_gate_scan(_ptr(z), _ptr(bias_i), _ptr(bias_f), ctypes.c_float(cap), _ptr(row_q_start), _ptr(row_q_len),
+                                           _ptr(state_slots), _ptr(m_state), _ptr(keep), _ptr(write), _ptr(m), row_q_len.numel(),
+                                           num_heads, _stream()), "gate_scan")
+    return keep, write, m
+
+
+def group_norm_gate(o: torch.Tensor, gate, out: torch.Tensor, *, groups: int, size: int, eps: float, weight=None, silu: bool = False,
+                    m=None) -> torch.Tensor:
+    """o float32 [T, groups * stride] (stride = size, or size + 1 with ``m``): each group of ``size`` entries is divided by
+    its root mean square, multiplied by ``weight`` (float32; indexed by the entry's place in the row modulo its length: size
+    entries shared by the groups, or groups * size) and by sigmoid (``silu``: silu) of ``gate`` [T, groups * size] (a column
+    slice of a wider tensor will do).  With ``m`` [T, groups]: the entry behind a group's outputs is a normalizer n and the
+    group is first divided by max(|n|, exp(-m)) + 1e-6.  groups = 1 norms the whole row."""
+    T = o.shape[0]
+    stride = size + (1 if m is not None else 0)
+    _need(o.dtype == torch.float32 and o.is_contiguous() and o.shape == (T, groups * stride), "o must be float32 [T, groups * (size (+ 1))]")
+    _need(out.is_contiguous() and out.shape == (T, groups * size), "out must be contiguous [T, groups * size]")
+    if gate is not None:
+        _need(gate.stride(1) == 1 and gate.shape == out.shape and gate.dtype == out.dtype, "gate must match the output's shape and type")
+    if weight is not None:
+        _need(weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() in (size, groups * size), "float32 weight of size or groups * size entries")
+    if m is not None:
+        _need(m.dtype == torch.float32 and m.is_contiguous() and m.shape == (T, groups), "m must be float32 [T, groups]")
+    _check(load("retention").mie_group_norm_gate(_ptr(o), stride, _ptr(m), _ptr(weight), weight.numel() if weight is not None else 0, _ptr(gate),
+                                                 tag(out), ctypes.c_longlong(gate.stride(0) if gate is not None else 0), _ptr(out), T, groups,
+                                                 size, ctypes.c_float(eps), int(m is not None), int(silu), _stream()), "group_norm_gate")
     return out
 
 
@@ -1020,7 +1176,9 @@ def head_norm_gate(o: torch.Tensor, gate, weight, out: torch.Tensor, num_heads: 
 
 # --------------------------------------------------------------------------- routed experts
 
-EXPERT_ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2}
+# "clamped_in" (gated experts only): the token's weight multiplies the expert's input; with g = min(w gate, limit), u = clamp(w up,
+# -limit, limit) the hidden value is g sigmoid(1.702 g) (u + 1), and nothing multiplies the output
+EXPERT_ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "clamped_in": 3}
 
 
 class RouteRule:
@@ -1031,10 +1189,12 @@ class RouteRule:
     none) are identity experts; the sum of their chosen weights is returned per token."""
 
     def __init__(self, score: str = "top_softmax", correction=None, groups: int = 1, keep: int = 1, real: int | None = None):
-        _need(score in ("top_softmax", "softmax"), f"router score {score!r}; one of top_softmax, softmax")
+        _need(score in ("top_softmax", "softmax", "sigmoid"), f"router score {score!r}; one of top_softmax, softmax, sigmoid")
         if correction is not None:
             _f32(correction, "router correction")
-        self.mode, self.correction, self.groups, self.keep, self.real = int(score == "softmax"), correction, int(groups), int(keep), real
+        # "sigmoid": the ``top`` largest logits, each chosen output's weight the sigmoid of its own logit (not renormalized)
+        self.mode = {"top_softmax": 0, "softmax": 1, "sigmoid": 2}[score]
+        self.correction, self.groups, self.keep, self.real = correction, int(groups), int(keep), real
 
     def args(self, outputs: int, tokens: int, device):
         """(ctypes arguments behind ``top``, the per-token rest weights or None)."""
@@ -1096,7 +1256,7 @@ def moe_pairs_fit(hidden: int, expert_size: int, top: int) -> bool:
 
 
 def moe_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids, wts, out: torch.Tensor, num_experts: int,
-              activation: str, gated: bool = False) -> torch.Tensor:
+              activation: str, gated: bool = False, limit: float = 0.0) -> torch.Tensor:
     """The routed experts for a handful of tokens: every (token, chosen expert) pair reads its expert's rows of the
     stacked matrices ``w_up`` [E * F, h] and ``w_down`` [h, E * F] and nothing else.  out [T, h] float32 = sum over the
     token's pairs of weight * W_down[e] f(W_up[e] x).  ``gated``: ``w_up`` is [E * 2F, h], per expert F gate rows then F up rows,
@@ -1114,7 +1274,7 @@ def moe_pairs(x: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids, wt
     hid = torch.empty(T * top, F, dtype=x.dtype, device=x.device)
     lib = load("moe")
     _check(lib.mie_moe_pairs(_ptr(x), tag(x), _ptr(w_up), _ptr(w_down), tag(w_up), _ptr(ids), _ptr(wts), _ptr(hid), _ptr(out), T, h,
-                             int(num_experts), F, top, EXPERT_ACTIVATIONS[activation], int(gated), _stream()), "moe_pairs")
+                             int(num_experts), F, top, EXPERT_ACTIVATIONS[activation], int(gated), ctypes.c_float(limit), _stream()), "moe_pairs")
     return out
 
 
@@ -1158,7 +1318,7 @@ def moe_combine(rows: torch.Tensor, place: torch.Tensor, top: int, out: torch.Te
     return out
 
 
-def moe_glu(gu: torch.Tensor, num_experts: int, activation: str, *, ids=None, wts=None, row_weight=None) -> torch.Tensor:
+def moe_glu(gu: torch.Tensor, num_experts: int, activation: str, *, ids=None, wts=None, row_weight=None, limit: float = 0.0) -> torch.Tensor:
     """The activation of gated experts.  With ``ids``/``wts`` [T, top] and ``gu`` [T, E * 2F] (per expert F gate then F up
     entries): act [T, E * F] = weight f(gate) up for the experts a token chose, 0 for the others.  With ``row_weight`` [R] and
     ``gu`` [R, 2F]: hid [R, F] = row_weight f(gate) up, row by row."""
@@ -1172,7 +1332,7 @@ def moe_glu(gu: torch.Tensor, num_experts: int, activation: str, *, ids=None, wt
           "float32 weights: one a row, or [T, top] beside int32 ids")
     act = torch.empty(R, E * F, dtype=gu.dtype, device=gu.device)
     _check(load("moe").mie_moe_glu(_ptr(gu), _ptr(ids), _ptr(w), _ptr(act), tag(gu), R, E, F, 0 if per_row else ids.shape[1],
-                                   EXPERT_ACTIVATIONS[activation], int(per_row), _stream()), "moe_glu")
+                                   EXPERT_ACTIVATIONS[activation], int(per_row), ctypes.c_float(limit), _stream()), "moe_glu")
     return act
 
 

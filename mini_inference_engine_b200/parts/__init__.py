@@ -1,4 +1,4 @@
-from . import attention, block, delta, embedding, feedforward, norm, parallel, recurrent, retention, rope  # noqa: F401  (registers the parts)
+from . import attention, block, delta, embedding, feedforward, matrix_memory, norm, parallel, recurrent, retention, rope  # noqa: F401  (registers the parts)
 from .block import Block, Branches
 from .base import (FeedForward, KVNeed, LayerCache, Mixer, Part, Runtime, StateNeed, StepContext, StreamValue, build_part,
                    part_class, register_part)

@@ -98,14 +98,34 @@ class GatedAttention(Mixer):
     * rotation over the first ``rot_dims`` dims with frequencies that may be rescaled by wavelength (``rot_scaling``);
     * ``head_temp``: the score of head h is multiplied by 'temp'[h] (folded into the query);
     * ``chunk``: a query sees keys of its own block of that many positions only; ``window``: a sliding window;
-    * ``gate``: the concatenated heads are multiplied by sigmoid(W_g h) before the output projection.
+    * ``gate``: the concatenated heads are multiplied by sigmoid(W_g h) before the output projection;
+    * ``bias``: q, k and v have biases 'q.b', 'k.b', 'v.b', added in the projection;
+    * ``qk_norm`` "head": the RMS norm is per head, with ``dim`` weights ('q.norm', 'k.norm') shared by all heads;
+    * ``rot_pairing`` "interleaved": the rotation pairs entry 2i with 2i + 1 (default: i with i + rot_dims / 2);
+    * ``q_temp`` (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1);
+    * ``softcap`` c: score <- c tanh(score / c) after the scale;
+    * ``rel_bias`` (rows, far): a learned bias 'rel' [rows, heads] by distance n = p - j is added to the (scaled, capped) score:
+      row n for n < rows / 2, else min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) (rows - rows/2)));
+      ``rows`` None: the table's rows come from the checkpoint's tensor (a random model gets 32);
+    * ``sink``: a learned number per head ('sink') whose exponential joins the softmax's denominator, with no key or value.
 
     q, k, v and the gate are one product; norm, rotation, temperature and the cache write one kernel; attention
     itself is the framework's paged kernels (decode and portions); the gate one more."""
 
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, dim: int, vdim: int, scale: float,
                  rot_dims: int, rot_base: float, eps: float, rot_scaling: dict | None = None, qk_norm: bool = True,
-                 head_temp: bool = True, gate: bool = True, chunk: int | None = None, window: int | None = None):
+                 head_temp: bool = True, gate: bool = True, chunk: int | None = None, window: int | None = None,
+                 bias: bool = False, rot_pairing: str = "half", q_temp=None, softcap: float = 0.0, rel_bias=None,
+                 sink: bool = False):
+        if rot_pairing not in ("half", "interleaved"):
+            raise ValueError(f"rot_pairing {rot_pairing!r}; half or interleaved")
+        if qk_norm not in (True, False, "head", "projection"):
+            raise ValueError(f"qk_norm {qk_norm!r}; False, True / 'projection' or 'head'")
+        if rel_bias is not None and rel_bias[0] is not None and (int(rel_bias[0]) < 2 or float(rel_bias[1]) <= int(rel_bias[0]) // 2):
+            raise ValueError(f"rel_bias {rel_bias!r}: two rows or more, and a far distance beyond half of them")
+        self.bias, self.rot_pairing, self.softcap, self.sink = bool(bias), rot_pairing, float(softcap or 0.0), bool(sink)
+        self.q_temp = (float(q_temp[0]), int(q_temp[1])) if q_temp else None
+        self.rel_bias = (int(rel_bias[0]) if rel_bias[0] is not None else None, float(rel_bias[1])) if rel_bias else None
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         if rot_dims % 2 or rot_dims > dim:
@@ -125,10 +145,19 @@ class GatedAttention(Mixer):
                  "o": TensorSpec((h, H * Dv), "fan_in")}
         if self.gate:
             specs["g"] = TensorSpec((H * Dv, h), "fan_in")
-        if self.qk_norm:
+        if self.qk_norm == "head":
+            specs.update({"q.norm": TensorSpec((D,), "normal:1:0.1"), "k.norm": TensorSpec((D,), "normal:1:0.1")})
+        elif self.qk_norm:
             specs.update({"q.norm": TensorSpec((H * D,), "normal:1:0.1"), "k.norm": TensorSpec((G * D,), "normal:1:0.1")})
         if self.head_temp:
             specs["temp"] = TensorSpec((H,), "uniform:0.5:2")
+        if self.bias:
+            specs.update({"q.b": TensorSpec((H * D,), "normal:0:0.1"), "k.b": TensorSpec((G * D,), "normal:0:0.1"),
+                          "v.b": TensorSpec((G * Dv,), "normal:0:0.1")})
+        if self.rel_bias:
+            specs["rel"] = TensorSpec((self.rel_bias[0] or -1, H), "normal:0:1", (self.rel_bias[0] or 32, H))
+        if self.sink:
+            specs["sink"] = TensorSpec((H,), "normal:0:1")
         return specs
 
     def bind(self, tensors, rt):
@@ -144,6 +173,27 @@ class GatedAttention(Mixer):
         self.k_norm = small("k.norm") if self.qk_norm else None
         self.temp = small("temp") if self.head_temp else None
         self.freq = rotary_frequencies(self.rot_dims, self.rot_base, self.rot_scaling).to(rt.device)
+        self.b_in = None
+        if self.bias:
+            b = torch.cat([tensors[n].float() for n in ("q.b", "k.b", "v.b")])
+            b = torch.cat([b, torch.zeros(self.w_in.shape[0] - b.numel())])          # the gate's rows have none
+            self.b_in = rt.place(b.to(torch.float32 if rt.dtype == torch.float32 else torch.bfloat16))
+        dist = None
+        if self.rel_bias:
+            # the bias by distance as a table over distances 0 .. far: the bucket of every distance is worked out here, once,
+            # in 64-bit; from ``far`` on the bucket no longer changes (the last row)
+            import math
+            rows, far = tensors["rel"].shape[0], self.rel_bias[1]
+            half = rows // 2
+            if rows < 2 or far <= half:
+                raise ValueError(f"a bias table of {rows} rows with a far distance of {far}")
+            bucket = lambda n: n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+            idx = torch.tensor([bucket(n) for n in range(int(math.ceil(far)) + 1)], dtype=torch.long)
+            dist = tensors["rel"].float()[idx].to(rt.device).contiguous()             # [far + 1, H]
+        from ..kernels import ops
+        self.mods = None
+        if self.softcap > 0 or self.sink or dist is not None:
+            self.mods = ops.ScoreMods(self.softcap, small("sink") if self.sink else None, dist)
 
     def cache_need(self):
         return self.need
@@ -160,13 +210,14 @@ class GatedAttention(Mixer):
         from ..kernels import ops
         H, G, D, Dv, DP = self.num_heads, self.num_kv_heads, self.dim, self.vdim, self.padded
         T = ctx.num_tokens
-        proj = self.rt.linear(x, self.w_in)
+        proj = self.rt.linear(x, self.w_in, self.b_in)
         q = self.rt.empty(T, H, DP)
         ops.qk_norm_rope(proj, ctx.positions, ctx.slots[cache.group], self.freq, q, cache.k, cache.v, num_heads=H,
                          num_kv_heads=G, dim=D, vdim=Dv, rot=self.rot_dims, page_size=cache.page_size, eps=self.eps,
-                         q_weight=self.q_norm, k_weight=self.k_norm, temp=self.temp, write_cache=cache.writes)
+                         q_weight=self.q_norm, k_weight=self.k_norm, temp=self.temp, write_cache=cache.writes,
+                         head_norm=self.qk_norm == "head", interleaved=self.rot_pairing == "interleaved", pos_temp=self.q_temp)
         heads = self.rt.empty(T, H, DP)
-        attn_kernels.attention(q, ctx, cache, heads, H, G, DP, self.scale, self.need.mask(), q_stride=H * DP)
+        attn_kernels.attention(q, ctx, cache, heads, H, G, DP, self.scale, self.need.mask(), q_stride=H * DP, mods=self.mods)
         if self.gate or DP != Dv:
             gated = self.rt.empty(T, H * Dv)
             if self.gate:

@@ -45,15 +45,21 @@ class Block(Part):
 
 
 class PreNormResidual(Block):
+    """``feed_forward`` (with its norm) may be absent: the layer is then its mixer half, and the mixer's output is what
+    the next reader of the stream adds."""
     roles = {"mixer": "mixer", "feed_forward": "feed_forward", "mixer_norm": "norm", "feed_forward_norm": "norm"}
+    optional_roles = ("feed_forward", "feed_forward_norm")
 
     def forward(self, delta, res, ctx, cache, next_block=None):
         """``next_block``: the block that runs after this one, if it reads the stream through a norm
         and a mixer as this one does (then the feed-forward may prepare that norm's output)."""
         n = res.shape[0]
         x = self.mixer_norm(delta, res)
-        sink = _sink_for(self.mixer, self.feed_forward, self.feed_forward_norm, res, n)
+        ff = getattr(self, "feed_forward", None)
+        sink = _sink_for(self.mixer, ff, getattr(self, "feed_forward_norm", None), res, n)
         a = self.mixer.forward(x, ctx, cache, sink) if sink is not None else self.mixer.forward(x, ctx, cache)
+        if ff is None:
+            return a
         x = self.feed_forward_norm(a, res)
         sink = _sink_for(self.feed_forward, getattr(next_block, "mixer", None), getattr(next_block, "mixer_norm", None), res, n)
         return self.feed_forward.forward(x, ctx, sink) if sink is not None else self.feed_forward.forward(x, ctx)
@@ -66,9 +72,60 @@ class Branches:
     """What a mixer may return instead of one tensor: several outputs that the block's norm adds together, each
     optionally RMS-normed over its row with ``inner_weights[k]`` first, the sum multiplied by ``coef``."""
 
-    def __init__(self, deltas, inner_weights=(), coef: float = 1.0, scaled=None):
+    def __init__(self, deltas, inner_weights=(), coef: float = 1.0, scaled=None, coefs=None):
         self.deltas, self.inner_weights, self.coef = tuple(deltas), tuple(inner_weights), coef
+        self.coefs = tuple(coefs) if coefs is not None else None      # a coefficient per output instead of one for the sum
         self.scaled = scaled            # (h [T, W], w float32 [T]): one more output, w[t] * h[t] (norms that add by ``add_to``)
+
+
+class StreamMix(Part):
+    """The stream mixed with the embedding's output e (which the embedding kept, ``ctx.extras["embedding_output"]``) and
+    shifted: x <- W [x; e] + b with W = 'in' [width, 2 width] (x's columns first) and b = row ``index`` of 'step' [rows,
+    width].  Models that run a stretch of layers several times put one in front of every pass, all sharing the two
+    tensors.  What the block before left to be added is added first, inside the kernel that joins the two streams for
+    the product; the product leaves float32 and becomes the stream."""
+
+    def __init__(self, hidden_size: int, rows: int, index: int):
+        if not 0 <= index < rows:
+            raise ValueError(f"shift {index} of {rows}")
+        self.hidden_size, self.rows, self.index = hidden_size, rows, index
+
+    def tensor_specs(self):
+        h = self.hidden_size
+        return {"in": TensorSpec((h, 2 * h), "fan_in"), "step": TensorSpec((self.rows, h), "normal:0:0.1")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.w_in = rt.place(tensors["in"])
+        self.shift = tensors["step"][self.index].float().to(rt.device).contiguous()
+
+    def kernel_sources(self):
+        return {"layer_norm"} | self.rt.product_sources(self.w_in)
+
+    def apply(self, delta, res, ctx):
+        from .norm import addends_of
+        e = ctx.extras.get("embedding_output")
+        if e is None:
+            raise ValueError("mixing the stream with the embedding's output needs an embedding that keeps it (keep_output)")
+        deltas, coefs = addends_of(delta)
+        joined = self.rt.empty(res.shape[0], 2 * self.hidden_size)
+        ops.stream_join(res, e, joined, deltas=deltas, coefs=coefs)
+        res.copy_(self.rt.linear(joined, self.w_in, self.shift, out_dtype=res.dtype))
+
+
+register_part("connection", "stream_mix", StreamMix)
+
+
+class StreamMixStep(Block):
+    """Not a layer but a step between layers: its one part rewrites the stream (``StreamMix``); nothing is left pending."""
+    roles = {"mix": "connection"}
+
+    def forward(self, delta, res, ctx, cache):
+        self.mix.apply(delta, res, ctx)
+        return None
+
+
+register_part("block", "stream_mix_step", StreamMixStep)
 
 
 class PostNormResidual(Block):

@@ -10,9 +10,12 @@ from .base import Part, register_part
 
 
 class Embedding(Part):
-    def __init__(self, vocab_size: int, hidden_size: int):
+    def __init__(self, vocab_size: int, hidden_size: int, keep_output: bool = False):
+        """``keep_output``: a copy of what the embedding leaves stays in ``ctx.extras["embedding_output"]`` for parts that
+        read it again later in the step (float32, as the stream)."""
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
+        self.keep_output = bool(keep_output)
 
     def tensor_specs(self):
         return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
@@ -26,16 +29,21 @@ class Embedding(Part):
 
     def forward(self, ctx):
         res = self.rt.empty(ctx.num_tokens, self.hidden_size, dtype=torch.float32)
-        return ops.embedding(self.weight, ctx.token_ids, res, ctx.token_feedback)
+        ops.embedding(self.weight, ctx.token_ids, res, ctx.token_feedback)
+        if self.keep_output:
+            ctx.extras["embedding_output"] = res.clone()
+        return res
 
 
 class LinearHead(Part):
-    """logits = x W^T in float32; ``tied`` takes W from the embedding (same tensor name)."""
+    """logits = x W^T in float32; ``tied`` takes W from the embedding (same tensor name).  ``softcap`` c > 0: the logits
+    become c tanh(logits / c)."""
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False):
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool = False, softcap: float = 0.0):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied = tied
+        self.softcap = float(softcap or 0.0)
 
     def tensor_specs(self):
         return {"weight": TensorSpec((self.vocab_size, self.hidden_size))}
@@ -45,10 +53,11 @@ class LinearHead(Part):
         self.weight = shared if shared is not None else rt.place(tensors["weight"])
 
     def kernel_sources(self):
-        return self.rt.product_sources(self.weight)
+        return self.rt.product_sources(self.weight) | ({"layer_norm"} if self.softcap > 0 else set())
 
     def forward(self, x):
-        return self.rt.linear(x, self.weight, None, out_dtype=torch.float32)
+        logits = self.rt.linear(x, self.weight, None, out_dtype=torch.float32)
+        return ops.tanh_cap(logits, self.softcap) if self.softcap > 0 else logits
 
 
 register_part("embedding", "embedding", Embedding)

@@ -154,7 +154,8 @@ class RoutedExperts(FeedForward):
     by expert over those rows (the library's grouped product), so no expert computes for a token that did not choose it."""
 
     def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, activation: str = "relu2", gated: bool = False,
-                 score: str = "top_softmax", correction: bool = False, groups: int = 1, keep: int = 1, identity: int = 0, shared=None):
+                 score: str = "top_softmax", correction: bool = False, groups: int = 1, keep: int = 1, identity: int = 0, shared=None,
+                 limit: float = 0.0):
         """``gated``: an expert is down(act(gate h) * (up h)) with a third matrix 'e<i>.gate'.  ``score`` "softmax": scores are
         the softmax over all router outputs, weights the chosen scores as they are; ``correction``: a tensor 'correction'
         [outputs] added to the scores for the choice only; ``groups`` / ``keep``: the outputs form that many equal groups of
@@ -162,7 +163,13 @@ class RoutedExperts(FeedForward):
         router outputs behind the experts' stand for "the input itself" (no matrices).  ``shared``: the PartSpec of a
         feed-forward that every token goes through ('shared.*'), added to the sum.  With identity experts or a shared one
         ``forward`` returns the outputs as ``Branches`` for the block's norm to sum."""
+        # ``score`` "sigmoid": the ``top`` largest logits are chosen and each weight is the sigmoid of its own logit, not
+        # renormalized.  ``activation`` "clamped_in" (gated experts): the weight multiplies the expert's input instead of its
+        # output, and the hidden value is g sigmoid(1.702 g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
         outputs = num_experts + identity
+        self.limit = float(limit or 0.0)
+        if activation == "clamped_in" and not gated:
+            raise ValueError("the clamped activation belongs to gated experts")
         if not 1 <= top <= outputs or num_experts < 1 or identity < 0:
             raise ValueError(f"top {top} of {num_experts} experts and {identity} identity experts")
         if activation not in ops.EXPERT_ACTIVATIONS:
@@ -170,6 +177,8 @@ class RoutedExperts(FeedForward):
         if groups > 1 and (score != "softmax" or outputs % groups or not 1 <= keep <= groups or groups > 64 or top > keep * (outputs // groups)):
             raise ValueError(f"{groups} groups (keep {keep}) over {outputs} router outputs with top {top}: groups must divide the outputs, "
                              "hold at least top outputs between the kept ones, and belong to the softmax score")
+        if score not in ("top_softmax", "softmax", "sigmoid"):
+            raise ValueError(f"router score {score!r}; one of top_softmax, softmax, sigmoid")
         if (correction or identity) and score != "softmax":
             raise ValueError("a correction and identity experts belong to the softmax score")
         self.hidden_size, self.num_experts, self.top, self.expert_size, self.activation = hidden_size, num_experts, top, expert_size, activation
@@ -209,7 +218,7 @@ class RoutedExperts(FeedForward):
         self.rule = None
         if self.score != "top_softmax" or self.identity:
             self.rule = ops.RouteRule(self.score, tensors["correction"].float().to(rt.device).contiguous() if self.correction else None,
-                                      self.groups, self.keep, self.num_experts)
+                                      self.groups, self.keep, self.num_experts if self.identity else None)
         if self.shared is not None:
             self.shared.bind({k: tensors["shared." + k] for k in self.shared.tensor_specs()}, rt)
         E, F, h = self.num_experts, self.expert_size, self.hidden_size
@@ -265,7 +274,7 @@ class RoutedExperts(FeedForward):
         T = x.shape[0]
         if self._pairs_serve(x):
             out = torch.empty(T, self.hidden_size, dtype=torch.float32, device=x.device)
-            return ops.moe_pairs(x, self.w_up, self.w_down, ids, wts, out, self.num_experts, self.activation, self.gated)
+            return ops.moe_pairs(x, self.w_up, self.w_down, ids, wts, out, self.num_experts, self.activation, self.gated, self.limit)
         # up to the token count that the framework's own streaming product serves, the wide form reads every expert once at
         # that kernel's rate, which the grouped product does not reach on so few rows
         if self.grouped and x.dtype == torch.bfloat16 and x.is_contiguous() and T > GROUPED_MIN_TOKENS:
@@ -273,14 +282,14 @@ class RoutedExperts(FeedForward):
             ends = ends[:self.num_experts]
             rows = ops.moe_gather(x, place, self.top)
             up = ops.grouped_linear(rows, self.b_up, ends)
-            hid = (ops.moe_glu(up, 1, self.activation, row_weight=row_weight) if self.gated
+            hid = (ops.moe_glu(up, 1, self.activation, row_weight=row_weight, limit=self.limit) if self.gated
                    else ops.moe_act_rows(up, row_weight, self.activation))
             down = ops.grouped_linear(hid, self.b_down, ends)
             return ops.moe_combine(down, place, self.top, torch.empty(T, self.hidden_size, dtype=torch.float32, device=x.device),
                                    ids if self.identity else None, self.num_experts)
         up = self.rt.linear(x, self.w_up)
         if self.gated:
-            act = ops.moe_glu(up, self.num_experts, self.activation, ids=ids, wts=wts)
+            act = ops.moe_glu(up, self.num_experts, self.activation, ids=ids, wts=wts, limit=self.limit)
         else:
             act = ops.moe_dense_act(up, ids, wts, torch.empty_like(up), self.num_experts, self.activation)
         return self.rt.linear(act, self.w_down, None, out_dtype=torch.float32)

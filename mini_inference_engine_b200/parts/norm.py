@@ -43,6 +43,48 @@ class RMSNorm(Part):
 register_part("norm", "rmsnorm", RMSNorm)
 
 
+def addends_of(delta):
+    """(tensors, coefficients) of what a sublayer left to be added to the stream: nothing, one output, or several
+    outputs with a coefficient each (``Branches`` without inner norms)."""
+    from .block import Branches
+    if delta is None or isinstance(delta, (StreamValue, StreamUpdated)):
+        return (), ()
+    if isinstance(delta, Branches):
+        if delta.inner_weights or delta.scaled is not None:
+            raise ValueError("this norm adds plain outputs with coefficients; the branches came with norms of their own")
+        return delta.deltas, delta.coefs if delta.coefs is not None else (delta.coef,) * len(delta.deltas)
+    return (delta,), (1.0,)
+
+
+class LayerNorm(Part):
+    """Layer norm with a weight and no bias, fused with the sum in front of it: ``res += sum_k c_k delta_k``, then
+    x = (res - mean) / sqrt(var + eps) * w with the variance as the mean of the squared deviations.  The addends are the
+    output of the sublayer before (float32) or the several outputs of mixers side by side with their coefficients.
+    ``center`` False leaves the mean out (an RMS norm over the same sums)."""
+
+    def __init__(self, size: int, eps: float, center: bool = True):
+        self.size, self.eps, self.center = size, eps, bool(center)
+
+    def tensor_specs(self):
+        return {"weight": TensorSpec((self.size,), "normal:1:0.1")}
+
+    def bind(self, tensors, rt):
+        self.rt = rt
+        self.weight = tensors["weight"].float().to(rt.device).contiguous()      # read as float32 by the kernel
+
+    def kernel_sources(self):
+        return {"layer_norm"}
+
+    def __call__(self, delta, res, rows=None):
+        deltas, coefs = addends_of(delta)
+        n_out = rows.numel() if rows is not None else res.shape[0]
+        out = self.rt.empty(n_out, self.size)
+        return ops.add_layernorm(res, self.weight, self.eps, out, deltas=deltas, coefs=coefs, rows=rows, center=self.center)
+
+
+register_part("norm", "layernorm", LayerNorm)
+
+
 class GroupRMSNorm(Part):
     """RMS norm with statistics per group: a row is cut into ``groups`` equal consecutive parts, each divided by
     sqrt(mean(part^2) + eps), and the whole multiplied by the weight.  It norms the stream itself (post-norm

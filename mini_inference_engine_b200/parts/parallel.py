@@ -25,11 +25,16 @@ def _side_stream(device):
 
 
 class ParallelMixers(Mixer):
-    def __init__(self, hidden_size: int, branches: dict):
+    def __init__(self, hidden_size: int, branches: dict, scales=None):
         """``branches``: {name: PartSpec of a mixer}; a branch's tensors are '<name>.<its own>', its out-norm weight
         '<name>.out'."""
         if not 1 <= len(branches) <= 2:
             raise ValueError("the norm kernel adds one or two branches")
+        # ``scales`` (one number per branch): the result is the weighted sum of the branches' outputs as they are -- no
+        # out-norms, no '<name>.out' tensors, no mean
+        if scales is not None and len(scales) != len(branches):
+            raise ValueError("one scale per branch")
+        self.scales = tuple(float(s) for s in scales) if scales is not None else None
         self.hidden_size = hidden_size
         self.names = list(branches)
         self.branches = [build_part("mixer", branches[n]) for n in self.names]
@@ -38,7 +43,8 @@ class ParallelMixers(Mixer):
         specs = {}
         for name, b in zip(self.names, self.branches):
             specs.update({f"{name}.{k}": v for k, v in b.tensor_specs().items()})
-            specs[f"{name}.out"] = TensorSpec((self.hidden_size,), "normal:1:0.1")
+            if self.scales is None:
+                specs[f"{name}.out"] = TensorSpec((self.hidden_size,), "normal:1:0.1")
         return specs
 
     def bind(self, tensors, rt):
@@ -46,7 +52,8 @@ class ParallelMixers(Mixer):
         self.out_weights = []
         for name, b in zip(self.names, self.branches):
             b.bind({k: tensors[f"{name}.{k}"] for k in b.tensor_specs()}, rt)
-            self.out_weights.append(tensors[f"{name}.out"].float().to(rt.device).contiguous())   # float32 for the norm kernel
+            if self.scales is None:
+                self.out_weights.append(tensors[f"{name}.out"].float().to(rt.device).contiguous())   # float32 for the norm kernel
 
     def cache_need(self):
         return tuple(b.cache_need() for b in self.branches)
@@ -77,6 +84,8 @@ class ParallelMixers(Mixer):
             outs = [first, second]
         else:
             outs = [b.forward(x, ctx, c) for b, c in zip(self.branches, cache.parts)]
+        if self.scales is not None:
+            return Branches(outs, coefs=self.scales)
         return Branches(outs, self.out_weights, coef=1.0 / len(outs))
 
 
