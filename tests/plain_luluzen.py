@@ -67,8 +67,15 @@ def router_choice(h, W, p, top):
     return idx, val
 
 
+MARGINS = None      # a list, while a caller wants them: per call of a router, per token the gap between the last chosen score and the next
+
+
 def routed_ff(h, W, p, mlp):
     idx, val = router_choice(h, W, p, int(mlp["router"]["top"]))
+    if MARGINS is not None and int(mlp["router"]["top"]) < int(mlp["router"]["experts"]):
+        s = torch.sigmoid(h @ W[p + "router"].T).sort(-1, descending=True).values
+        k = int(mlp["router"]["top"])
+        MARGINS.append(s[:, k - 1] - s[:, k])
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(idx[t].tolist(), val[t]):
@@ -287,6 +294,21 @@ def run_order(cfg):
     for t in range(times):
         order += [(i, t if i == lo else None) for i in range(lo, hi)]
     return order + [(i, None) for i in range(hi, n)]
+
+
+def choice_margins(cfg, W, tokens):
+    """Per token, the smallest gap over all its routers between the last chosen expert's score and the best one left out
+    (infinity where no router chooses): how close the token came to another choice of experts."""
+    global MARGINS
+    MARGINS = []
+    try:
+        forward(cfg, W, tokens)
+        out = torch.full((len(tokens),), float("inf"))
+        for m in MARGINS:
+            out = torch.minimum(out, m.float())
+        return out
+    finally:
+        MARGINS = None
 
 
 def forward(cfg, W, tokens, trace=None):
