@@ -451,11 +451,34 @@ def serotar_configs(size: dict, vocab=32000, positions=4096):
     return serotar, design_configs(size, vocab, positions)[1]
 
 
+def luluzen_configs(size: dict, vocab=32000, positions=4096):
+    """A Luluzen configuration of the given layer sizes -- lightning attention with a gelu-gated feed-forward, then a stretch
+    that runs twice: windowed, capped attention with a sink beside a matrix memory, and attention with a bias by distance
+    beside the gated delta rule, both with sixteen experts of which a token uses four (sized so that the matrices a token
+    goes through equal Llama's three), then lightning attention again: six layer runs -- and the Llama configuration with the
+    same width, heads and number of layers."""
+    from mini_inference_engine_b200.config import load_config
+    w, ff, H, G, R = size["width"], size["ff"], size["heads"], size["kv_heads"], size["ret_heads"]
+    moe = dict(kind="moe", expert=dict(ff=(ff // 4 + 63) // 64 * 64, limit=7.0), router=dict(experts=16, top=4))
+    light = dict(type="lightning", mlp=dict(kind="dense", ff=ff), mixer=dict(heads=R, dim=128, vdim=256,
+                 decay=[1.0 - 2.0 ** (-5 - i % 8) for i in range(R)]))
+    par2 = dict(type="parallel_2", mlp=moe, mixer=dict(left_scale=1.0, right_scale=1.0,
+                left=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, softcap=30.0, mask=dict(size=1024), rot=dict(base=5e5, dims=64)),
+                right=dict(heads=R, dim=128, vdim=256, gate_cap=15.0)))
+    par = dict(type="parallel", mlp=moe, mixer=dict(left_scale=1.0, right_scale=1.0,
+               left=dict(heads=H, kv_heads=G, dim=128, vdim=128, scale=128 ** -0.5, bias_max=1024, q_temp=dict(coef=0.1, every=512)),
+               right=dict(heads=H, kv_heads=H, dim=128, vdim=128, conv=4)))
+    luluzen = load_config(dict(architecture="Luluzen", vocab=vocab, width=w, norm=dict(eps=1e-5), logit_softcap=30.0,
+                               loop=dict(start=1, stop=3, times=2), layers=[light, par2, par, light]))
+    return luluzen, design_configs(size, vocab, positions)[1]
+
+
 KERNEL_FACES = ("embedding", "add_rmsnorm", "stream_norm", "rope_cache_write", "qk_norm_rope", "paged_attention", "prefill_attention",
                 "prefill_attention_tc", "decode_attention", "retention_scan", "head_rms_gate", "causal_conv", "recurrence_gates",
                 "recurrence_scan", "swiglu", "glu_clamped", "sigmoid_gate", "hyper_norm", "latent_norm_rope", "latent_assemble",
                 "diff_combine", "delta_prepare", "conv_state_update", "delta_scan", "head_norm_gate", "moe_route", "moe_router", "moe_dense_act", "moe_pairs", "moe_sort", "moe_gather", "moe_act_rows", "moe_combine", "grouped_linear",
-                "pair_embedding", "normed_add", "xielu", "gelu_gate_rows", "moe_glu")
+                "pair_embedding", "normed_add", "xielu", "gelu_gate_rows", "moe_glu", "add_layernorm", "stream_join", "tanh_cap",
+                "decay_scan", "gate_scan", "group_norm_gate")
 
 
 class KernelTimes:
@@ -510,7 +533,7 @@ def run_design(args, steps, warmup):
     from mini_inference_engine_b200 import EngineConfig, LLMEngine
     from mini_inference_engine_b200.weights import write_model_folder
     pk = peaks()
-    configs_for = {"getizen": design_configs, "kebudra": kebudra_configs, "serotar": serotar_configs}[args.design]
+    configs_for = {"getizen": design_configs, "kebudra": kebudra_configs, "serotar": serotar_configs, "luluzen": luluzen_configs}[args.design]
     out = {"metric": "design_comparison", "design": args.design.capitalize(), "beside": "Llama", "dtype": "bf16", "data": "synthetic (random weights, seed 0)",
            "peaks": pk, "sizes": {}}
     batches = [int(b) for b in args.points.split(",") if b] or [8]
@@ -576,7 +599,7 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--preset", default="tinyllama-1.1b")
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
-    ap.add_argument("--design", default=None, choices=["getizen", "kebudra", "serotar"],
+    ap.add_argument("--design", default=None, choices=["getizen", "kebudra", "serotar", "luluzen"],
                     help="instead of the default workload: prefill and decode throughput of this design beside Llama at equal "
                          "layer sizes (--sizes), random weights; decode batches from --points")
     ap.add_argument("--sizes", default="w2048,w4096", help="with --design: layer sizes to measure, of " + ", ".join(DESIGN_SIZES))

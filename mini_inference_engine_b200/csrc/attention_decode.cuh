@@ -320,7 +320,7 @@ decode_attention_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_
                     float v = s[n][i] * p.scale_log2e;
                     if (p.modded) {
                         const int gi = min(quad + 8 * (i >> 1), gn - 1);      // rows beyond the group's heads are never written
-                        v = mod_score(s[n][i] * p.scale, p.mods, kvh * G + g0 + gi, p.num_heads,
+                        v = mod_score<true>(s[n][i] * p.scale, p.mods, kvh * G + g0 + gi, p.num_heads,
                                       ctx - 1 - (key0 + n * 8 + tq * 2 + (i & 1))) * 1.4426950408889634f;
                     }
                     if (!whole) {

@@ -164,7 +164,7 @@ prefill_attention_kernel(const PrefillParams p) {
                 for (int i = 0; i < 4; ++i) {
                     float v = s[n][i] * p.scale_log2e;
                     if (p.modded)
-                        v = mod_score(s[n][i] * p.scale, p.mods, head, p.num_heads, qpos[i >> 1] - (key0 + n * 8 + tq * 2 + (i & 1))) * 1.4426950408889634f;
+                        v = mod_score<true>(s[n][i] * p.scale, p.mods, head, p.num_heads, qpos[i >> 1] - (key0 + n * 8 + tq * 2 + (i & 1))) * 1.4426950408889634f;
                     if (need_mask) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
                         const int qp = qpos[i >> 1];

@@ -50,6 +50,8 @@ struct FaParams {
     float scale_log2e;
     int64_t check_pages;     // pages in each cache, for the range check of block-table entries
     int* report;             // range report (range_check.cuh)
+    float scale;             // the scale without the base-2 factor, for scores that are modified before the softmax
+    ScoreMods mods;          // cap, bias by distance, sink (common.cuh): the kernel's MODS instance applies them
 };
 
 // MN-major B operand tile with the 128-byte swizzle: 64 elements of N contiguous in a 128-byte row,
@@ -101,8 +103,11 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-template <int D>
-__global__ void __launch_bounds__(FA_THREADS, 2)       // two blocks per SM: at most 168 registers
+// MODS: scores pass ScoreMods (a cap, a bias by distance) between the product and the softmax, and a sink may join the sum;
+// an instance of its own, so that the plain softmax keeps its instruction count.
+template <int D, bool MODS>
+__global__ void __launch_bounds__(FA_THREADS, MODS ? 1 : 2)       // two blocks per SM: at most 168 registers (the instance with
+                                                                  // modified scores needs more and takes an SM alone)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv activation [tokens, q_stride], box {64, 128}
                             const __grid_constant__ CUtensorMap map_k,   // key pages as rows [pages * kv_heads * page_size, D], box {64, page rows}
                             const __grid_constant__ CUtensorMap map_v,
@@ -342,6 +347,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 const int g0 = u ? nA : 0;                             // key tiles counted through both query tiles
                 const int qpos = pos0 + r;
                 float m_run = -INFINITY, l_run = 0.f;
+                if (MODS && p.mods.sink) { m_run = p.mods.sink[head] * 1.4426950408889634f; l_run = 1.f; }      // the sink: a term with no value
+                // a modified score in base 2, from the raw product and the key's position
+                auto score2 = [&](uint32_t raw, int key) {
+                    return mod_score<true>(__uint_as_float(raw) * p.scale, p.mods, head, p.num_heads, qpos - key) * 1.4426950408889634f;
+                };
                 for (int t = 0; t < ntiles && ok; ++t) {
                     const int g = g0 + t;
                     ok = __all_sync(0xffffffffu, mbar_wait(&s_full, g & 1, abort_p));     // the warp goes on or gives up as one
@@ -381,7 +391,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                         for_each_chunk([&](int ch, const uint32_t* c) {
     #pragma unroll
                             for (int i = 0; i < 32; ++i) {
-                                float x = __uint_as_float(c[i]);
+                                float x = MODS ? score2(c[i], key0 + ch * 32 + i) : __uint_as_float(c[i]);
                                 if (MASK && masked(key0 + ch * 32 + i)) x = -INFINITY;
                                 mx4[i & 3] = fmaxf(mx4[i & 3], x);
                             }
@@ -390,7 +400,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                     };
                     if (t == 0) {
                         const float mx = need_mask ? row_max(std::true_type{}) : row_max(std::false_type{});
-                        m_run = mx * p.scale_log2e;                    // the scale is positive: max and scaling commute
+                        const float m0 = MODS ? fmaxf(mx, m_run) : mx * p.scale_log2e;    // the scale is positive: max and scaling commute
+                        if (MODS && l_run > 0.f) l_run = ex2_approx(m_run - m0);          // the sink's term against the new reference
+                        m_run = m0;
                     }
                     float alpha = 1.f, sum = 0.f;
                     auto p_pass = [&](auto mask_tag, float neg_m, float& xmax_out) {
@@ -404,8 +416,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                             if (ch == 0 && g > 0 && !__all_sync(0xffffffffu, mbar_wait(&kv_empty[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_p))) ok = false;
     #pragma unroll
                             for (int i = 0; i < 32; i += 2) {
-                                float x0 = fmaf(__uint_as_float(c[i]), p.scale_log2e, neg_m);
-                                float x1 = fmaf(__uint_as_float(c[i + 1]), p.scale_log2e, neg_m);
+                                float x0 = MODS ? score2(c[i], key0 + ch * 32 + i) + neg_m : fmaf(__uint_as_float(c[i]), p.scale_log2e, neg_m);
+                                float x1 = MODS ? score2(c[i + 1], key0 + ch * 32 + i + 1) + neg_m : fmaf(__uint_as_float(c[i + 1]), p.scale_log2e, neg_m);
                                 if (MASK) {
                                     if (masked(key0 + ch * 32 + i)) x0 = -INFINITY;
                                     if (masked(key0 + ch * 32 + i + 1)) x1 = -INFINITY;
@@ -905,11 +917,11 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_
 
 static int g_fa_pp_mode = -1;
 
-template <int D>
+template <int D, bool MODS>
 static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int work_tokens,
                      int work_rows, cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * 128 * 64 * 2 * 6 + 1024;     // 2 x Q + 2 x (K + V)
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D, MODS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     // tiles <= tokens / 128 + rows (of the rows that this kernel serves, where the caller knows them); a block takes
     // one tile, or a pair of them (at most (tiles + rows) / 2 pairs) once the tiles of all heads are more than the
@@ -918,7 +930,7 @@ static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtenso
     FaParams pp = p;
     pp.pair = (int64_t)tiles * p.num_heads > (int64_t)device_sm_count() * (D == 64 ? 2 : 1);
     const dim3 grid(pp.pair ? (tiles + work_rows + 1) / 2 : tiles, p.num_heads);
-    return launch_kernel(prefill_attention_tc_kernel<D>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, pp);
+    return launch_kernel(prefill_attention_tc_kernel<D, MODS>, grid, dim3(FA_THREADS), smem, stream, mq, mk, mv, pp);
 }
 
 // q: the fused qkv activation [num_tokens, q_stride] bfloat16 (query head h at columns h*D ..), caches
@@ -930,7 +942,8 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
                                         int64_t num_pages, const int* block_tables, int table_stride, const int* row_q_start,
                                         const int* row_q_len, const int* row_ctx_len, int num_rows, int num_tokens, void* out,
                                         int num_heads, int num_kv_heads, int head_dim, int page_size, float scale, int window,
-                                        int min_q_len, int work_rows, int work_tokens, int out_f32, cudaStream_t stream) {
+                                        int min_q_len, int work_rows, int work_tokens, int out_f32, float softcap, const float* sink,
+                                        const float* dist_bias, int dist_len, cudaStream_t stream) {
     if (num_rows <= 0 || num_tokens <= 0) return 0;
     if (work_rows <= 0 || work_tokens <= 0 || work_rows > num_rows || work_tokens > num_tokens) { work_rows = num_rows; work_tokens = num_tokens; }
     if (head_dim != 64 && head_dim != 128) return MIE_ERR_BAD_ARG;
@@ -949,6 +962,10 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     while ((1 << p.page_shift) < page_size) ++p.page_shift;
     p.window = window; p.min_q_len = min_q_len; p.pair = 0;
     p.scale_log2e = scale * 1.4426950408889634f;
+    p.scale = scale;
+    p.mods = ScoreMods{softcap, sink, dist_bias, dist_len};
+    if (dist_bias && dist_len <= 0) return MIE_ERR_BAD_ARG;
+    const bool mods = softcap > 0.f || sink || dist_bias;
     p.check_pages = num_pages; p.report = g_range_report;
     CUtensorMap mq, mk, mv;
     const int box_rows = page_size < FA_BN ? page_size : FA_BN;
@@ -956,6 +973,8 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     if ((rc = make_map_2d(&mq, q, (uint64_t)num_tokens, (uint64_t)q_stride, (uint64_t)q_stride, FA_BM))) return rc;
     if ((rc = make_map_2d(&mk, k_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
     if ((rc = make_map_2d(&mv, v_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
+    if (mods) return head_dim == 64 ? launch_fa<64, true>(mq, mk, mv, p, work_tokens, work_rows, stream)
+                                    : launch_fa<128, true>(mq, mk, mv, p, work_tokens, work_rows, stream);
     if (head_dim == 64) {
         // two query tiles side by side once there are three pairs for every SM (measured, 32 heads, one tile a block
         // against two side by side: 2,048 tokens 45.1 against 48.5 us, 4,096 tokens 143.7 against 142.4 us, 8,192 tokens
@@ -964,9 +983,9 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
         if ((tiles + 2 * work_rows) / 2 < 65535 &&
             (g_fa_pp_mode == 1 || (g_fa_pp_mode < 0 && tiles * num_heads >= 6 * (int64_t)device_sm_count())))
             return launch_fa_pp(mq, mk, mv, p, work_tokens, work_rows, stream);
-        return launch_fa<64>(mq, mk, mv, p, work_tokens, work_rows, stream);
+        return launch_fa<64, false>(mq, mk, mv, p, work_tokens, work_rows, stream);
     }
-    return launch_fa<128>(mq, mk, mv, p, work_tokens, work_rows, stream);
+    return launch_fa<128, false>(mq, mk, mv, p, work_tokens, work_rows, stream);
 }
 
 // Which kernel serves head_dim 64: -1 chooses by the size of the launch (the default), 0 always one query tile a block,

@@ -393,30 +393,49 @@ extern "C" int mie_head_rms_gate(const float* o, const void* g, int tag, long lo
 //   i_t = cap tanh((zi_t + bi) / cap)          f_t = logsigmoid(cap tanh((zf_t + bf) / cap))        (cap <= 0: no cap)
 //   m_t = max(f_t + m_{t-1}, i_t)              keep_t = exp(f_t + m_{t-1} - m_t)      write_t = exp(i_t - m_t)
 // z [T, 2H] float32 holds [zi: H | zf: H] per token; m_state [slots, H] carries m between steps (0 for a fresh request).
-// One thread per (row, head) walks the row's tokens in order: the chain is a handful of scalar operations a token.
+// A warp per (row, head) takes 32 tokens at a time: with L_j the sum of f over the tile up to token j and m_c the maximum carried
+// into the tile, m_j - L_j = max(m_c, max over s <= j of (i_s - L_s)), so a prefix sum and a prefix maximum by shuffles give all 32
+// maxima at once, and the sums never run over more than a tile (no large numbers are subtracted from one another).
 __global__ void gate_scan_kernel(const float* __restrict__ z, const float* __restrict__ bi, const float* __restrict__ bf, float cap,
                                  const int* __restrict__ row_q_start, const int* __restrict__ row_q_len,
                                  const int* __restrict__ state_slots, float* __restrict__ m_state, float* __restrict__ keep,
                                  float* __restrict__ write, float* __restrict__ m_out, int num_rows, int H) {
     pdl_enter();
-    const int item = blockIdx.x * blockDim.x + threadIdx.x;
+    const int lane = threadIdx.x & 31;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (item >= num_rows * H) return;
     const int r = item / H, h = item - r * H;
     const int start = row_q_start[r], len = row_q_len[r];
     float* ms = m_state + (int64_t)state_slots[r] * H + h;
-    float m = *ms;
+    float m_c = *ms;
     const float b_i = bi ? bi[h] : 0.f, b_f = bf ? bf[h] : 0.f, inv = cap > 0.f ? 1.0f / cap : 0.f;
-    for (int t = start; t < start + len; ++t) {
-        float zi = z[(int64_t)t * 2 * H + h] + b_i, zf = z[(int64_t)t * 2 * H + H + h] + b_f;
-        if (cap > 0.f) { zi = cap * tanhf(zi * inv); zf = cap * tanhf(zf * inv); }
-        const float f = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));           // log sigmoid
-        const float m_new = fmaxf(f + m, zi);
-        keep[(int64_t)t * H + h] = expf(f + m - m_new);
-        write[(int64_t)t * H + h] = expf(zi - m_new);
-        m_out[(int64_t)t * H + h] = m_new;
-        m = m_new;
+    for (int t0 = 0; t0 < len; t0 += 32) {
+        const bool ok = t0 + lane < len;
+        const int64_t t = start + t0 + lane;
+        float gi = -INFINITY, f = 0.f;                         // lanes beyond the row: nothing is written, nothing forgotten
+        if (ok) {
+            float zi = z[t * 2 * H + h] + b_i, zf = z[t * 2 * H + H + h] + b_f;
+            if (cap > 0.f) { zi = cap * tanhf(zi * inv); zf = cap * tanhf(zf * inv); }
+            gi = zi;
+            f = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));     // log sigmoid
+        }
+        float L = f;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float up = __shfl_up_sync(0xffffffffu, L, o); if (lane >= o) L += up; }
+        float a = gi - L;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float up = __shfl_up_sync(0xffffffffu, a, o); if (lane >= o) a = fmaxf(a, up); }
+        const float m = L + fmaxf(m_c, a);
+        float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
+        if (lane == 0) m_prev = m_c;
+        if (ok) {
+            keep[t * H + h] = expf(f + m_prev - m);
+            write[t * H + h] = expf(gi - m);
+            m_out[t * H + h] = m;
+        }
+        m_c = __shfl_sync(0xffffffffu, m, min(31, len - t0 - 1));
     }
-    *ms = m;
+    if (lane == 0) *ms = m_c;
 }
 
 extern "C" int mie_gate_scan(const float* z, const float* bi, const float* bf, float cap, const int* row_q_start, const int* row_q_len,
@@ -424,8 +443,8 @@ extern "C" int mie_gate_scan(const float* z, const float* bi, const float* bf, f
                              cudaStream_t stream) {
     if (num_rows <= 0) return 0;
     if (H <= 0) return MIE_ERR_BAD_ARG;
-    const int items = num_rows * H, threads = 64;
-    return launch_kernel(gate_scan_kernel, dim3((items + threads - 1) / threads), dim3(threads), 0, stream, z, bi, bf, cap, row_q_start,
+    const int items = num_rows * H, warps = 2;
+    return launch_kernel(gate_scan_kernel, dim3((items + warps - 1) / warps), dim3(warps * 32), 0, stream, z, bi, bf, cap, row_q_start,
                          row_q_len, state_slots, m_state, keep, write, m_out, num_rows, H);
 }
 

@@ -62,8 +62,7 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
     where ``rotates_in_decode`` holds.  ``window``: None or 0 all earlier keys, w > 0 the last w positions, w < 0 the
     keys of the query's own block of -w positions.  ``q_stride``: elements between the token rows of ``qkv`` (by
     default rows of a fused q|k|v projection).  ``mods`` (``ops.ScoreMods``): a cap on the scores, a bias by distance, a sink in
-    the softmax; the CUDA-core, decode and mma.sync kernels apply them, so portions with head sizes 64 and 128 go to the
-    mma.sync kernel when a layer has any."""
+    the softmax; every kernel applies them (the tcgen05 kernel for portions in an instance of its own)."""
     if q_stride is None:
         q_stride = (num_heads + 2 * num_kv_heads) * head_dim
     args = (qkv, q_stride, cache.k, cache.v, ctx.block_tables[cache.group], ctx.row_q_start, ctx.row_q_len,
@@ -96,10 +95,10 @@ def attention(qkv, ctx, cache, out, num_heads, num_kv_heads, head_dim, scale, wi
                              max_ctx=reach, mods=mods)
     if has_prefill:
         # tcgen05 (S and O in tensor memory) for the head sizes it is written for, mma.sync otherwise
-        tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05" and mods is None
+        tc = head_dim in (64, 128) and cache.page_size >= 8 and q_stride % 8 == 0 and _prefill_backend == "tcgen05"
         fn = ops.prefill_attention_tc if tc else ops.prefill_attention
         # the rows that are portions, and their tokens: the launch is laid out for those, not for every decoding row
         work = None if kinds is None else (kinds[1], kinds[2])
         fn(*args, ctx.num_tokens, out, num_heads, num_kv_heads, head_dim, cache.page_size, scale, window,
-           min_q_len=min_q_len, work=work, **({} if tc else {"mods": mods}))
+           min_q_len=min_q_len, work=work, mods=mods)
     return out

@@ -416,7 +416,7 @@ def prefill_attention(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_ta
 def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block_tables, row_q_start, row_q_len,
                          row_ctx_len, num_tokens: int, out: torch.Tensor, num_heads: int, num_kv_heads: int,
                          head_dim: int, page_size: int, scale: float, window: int | None = None,
-                         min_q_len: int = 2, work=None) -> torch.Tensor:
+                         min_q_len: int = 2, work=None, mods: ScoreMods | None = None) -> torch.Tensor:
     """Causal attention of prompt portions on tcgen05 (S and O in tensor memory, operands by TMA);
     head_dim 64 or 128.  ``work``: as for ``prefill_attention``."""
     _need(q.dtype == torch.bfloat16 == k_cache.dtype == v_cache.dtype and out.dtype in (torch.bfloat16, torch.float32),
@@ -434,7 +434,7 @@ def prefill_attention_tc(q: torch.Tensor, q_stride: int, k_cache, v_cache, block
                                         _ptr(row_q_start), _ptr(row_q_len), _ptr(row_ctx_len), row_q_len.numel(),
                                         num_tokens, _ptr(out), num_heads, num_kv_heads, head_dim, page_size,
                                         ctypes.c_float(scale), int(window or 0), int(min_q_len), *_work_args(work),
-                                        int(out.dtype == torch.float32), _stream()),
+                                        int(out.dtype == torch.float32), *(mods or _NO_MODS).args(num_heads), _stream()),
            "prefill_attention_tc")
     return out
 

@@ -127,9 +127,26 @@ def test_bias_table_by_distance_follows_the_bucket_rule():
             assert table[min(n, table.shape[0] - 1), 0] == pz.distance_bucket(n, rows, far), (rows, far, n)
 
 
-def test_preset_and_benchmark_pair():
-    from mini_inference_engine_b200.config import load_preset
+def test_preset_and_the_benchmark_pair_of_equal_size():
+    """The shipped tiny preset reads back, and bench.py's --design option builds a Luluzen and a Llama configuration of the
+    same width, heads and number of layer runs, the feed-forward matrices a token goes through as large as Llama's three."""
+    import importlib.util
+
+    from mini_inference_engine_b200.config import load_preset, preset_names
+    assert "tiny-luluzen" in preset_names()
     cfg = load_preset("tiny-luluzen")
     assert type(cfg).__name__ == "LuluzenConfig" and cfg.loop is not None
-    kinds = {l["type"] for l in cfg.layers}
-    assert kinds == {"lightning", "parallel", "parallel_2"}
+    assert {l["type"] for l in cfg.layers} == {"lightning", "parallel", "parallel_2"}
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_for_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for size in bench.DESIGN_SIZES.values():
+        z, l = bench.luluzen_configs(size)
+        assert z.width == l.hidden_size == size["width"] and len(z.run_plan()) == l.num_hidden_layers == size["layers"]
+        assert {x["type"] for x in z.layers} == {"lightning", "parallel", "parallel_2"}
+        mlp = z.layers[1]["mlp"]
+        used = mlp["router"]["top"] * mlp["expert"]["ff"] * 3
+        assert abs(used - 3 * l.intermediate_size) <= 0.05 * 3 * l.intermediate_size
+        left = z.layers[1]["mixer"]["left"]
+        assert left["heads"] == l.num_attention_heads and left["dim"] == l.head_dim

@@ -166,13 +166,20 @@ def check(name, folder, dtype_name, got, reqs):
     another expert than the unrounded plain implementation (positions where the plain choice hung on a score gap under 0.05
     are not compared), and the first positions of a sequence, where the matrix memory's read-out is small beside the norm's
     eps and a per cent of difference in the input comes out eightfold in the plain implementation too; rows that follow
-    such a token read its keys, values and states.  So in bfloat16 the typical row must be close (the median error under
+    such a token read its keys, values and states.  (In float32 the same holds for a gap under 1e-4: a request is compared up to
+    its first such position.)  So in bfloat16 the typical row must be close (the median error under
     half the bound) and at most three rows in ten may be beyond the bound."""
     bad, errs = [], []
     for rid, toks in reqs.items():
         assert sorted(got[rid]) == list(range(len(toks))), f"{rid}: positions missing"
         want = plain_logits(name, folder, toks).numpy()
-        sure = np.ones(len(toks), dtype=bool) if dtype_name == "float32" else plain_margins(name, folder, toks) >= 0.05
+        margins = plain_margins(name, folder, toks)
+        sure = margins >= 0.05
+        if dtype_name == "float32":            # a choice that hangs on a gap of the size of float32's rounding may fall the other way, and
+            sure = np.ones(len(toks), dtype=bool)      # the tokens behind read that token's keys, values and states: compared up to it
+            close_calls = np.nonzero(margins < 1e-4)[0]
+            if close_calls.size:
+                sure[close_calls[0]:] = False
         for p in range(len(toks)):
             d = got[rid][p] - want[p]
             assert np.isfinite(d).all(), f"{name} {dtype_name} {rid}: position {p} is not finite"
