@@ -103,9 +103,10 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
-// MODS: scores pass ScoreMods (a cap, a bias by distance) between the product and the softmax, and a sink may join the sum;
-// an instance of its own, so that the plain softmax keeps its instruction count.
-template <int D, bool MODS>
+// MODS: what scores pass between the product and the softmax (ScoreMods): bit 0 a cap, bit 1 a bias by distance; an instance
+// for each combination, so that the plain softmax keeps its instruction count and the others test nothing per element.  A sink
+// joins the sum in every instance (it costs a term at a row's start).
+template <int D, int MODS>
 __global__ void __launch_bounds__(FA_THREADS, MODS ? 1 : 2)       // two blocks per SM: at most 168 registers (the instance with
                                                                   // modified scores needs more and takes an SM alone)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv activation [tokens, q_stride], box {64, 128}
@@ -347,10 +348,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                 const int g0 = u ? nA : 0;                             // key tiles counted through both query tiles
                 const int qpos = pos0 + r;
                 float m_run = -INFINITY, l_run = 0.f;
-                if (MODS && p.mods.sink) { m_run = p.mods.sink[head] * 1.4426950408889634f; l_run = 1.f; }      // the sink: a term with no value
+                if (p.mods.sink) { m_run = p.mods.sink[head] * 1.4426950408889634f; l_run = 1.f; }      // the sink: a term with no value
                 // a modified score in base 2, from the raw product and the key's position
+                const float cap2 = p.mods.softcap * 1.4426950408889634f, in_cap = (MODS & 1) ? p.scale / p.mods.softcap : 0.f;
+                const float* bias_h = (MODS & 2) ? p.mods.dist_bias + (int64_t)head * p.mods.dist_len : nullptr;
+                const unsigned last_dist = (unsigned)(p.mods.dist_len - 1);
                 auto score2 = [&](uint32_t raw, int key) {
-                    return mod_score<true>(__uint_as_float(raw) * p.scale, p.mods, head, p.num_heads, qpos - key) * 1.4426950408889634f;
+                    float x = __uint_as_float(raw);
+                    x = (MODS & 1) ? cap2 * tanh_fast(x * in_cap) : x * p.scale_log2e;
+                    // (a key behind the query has a negative distance: as an unsigned number it is clamped like a far one; its score is masked)
+                    if (MODS & 2) x = fmaf(bias_h[min((unsigned)(qpos - key), last_dist)], 1.4426950408889634f, x);
+                    return x;
                 };
                 for (int t = 0; t < ntiles && ok; ++t) {
                     const int g = g0 + t;
@@ -400,8 +408,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q,   // qkv 
                     };
                     if (t == 0) {
                         const float mx = need_mask ? row_max(std::true_type{}) : row_max(std::false_type{});
-                        const float m0 = MODS ? fmaxf(mx, m_run) : mx * p.scale_log2e;    // the scale is positive: max and scaling commute
-                        if (MODS && l_run > 0.f) l_run = ex2_approx(m_run - m0);          // the sink's term against the new reference
+                        const float m0 = fmaxf(MODS ? mx : mx * p.scale_log2e, m_run);      // the scale is positive: max and scaling commute
+                        if (l_run > 0.f) l_run = ex2_approx(m_run - m0);                  // the sink's term against the new reference
                         m_run = m0;
                     }
                     float alpha = 1.f, sum = 0.f;
@@ -917,7 +925,7 @@ static int make_map_2d(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_
 
 static int g_fa_pp_mode = -1;
 
-template <int D, bool MODS>
+template <int D, int MODS>
 static int launch_fa(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const FaParams& p, int work_tokens,
                      int work_rows, cudaStream_t stream) {
     const size_t smem = (size_t)(D / 64) * 128 * 64 * 2 * 6 + 1024;     // 2 x Q + 2 x (K + V)
@@ -965,7 +973,7 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     p.scale = scale;
     p.mods = ScoreMods{softcap, sink, dist_bias, dist_len};
     if (dist_bias && dist_len <= 0) return MIE_ERR_BAD_ARG;
-    const bool mods = softcap > 0.f || sink || dist_bias;
+    const int mods = (softcap > 0.f ? 1 : 0) | (dist_bias ? 2 : 0);
     p.check_pages = num_pages; p.report = g_range_report;
     CUtensorMap mq, mk, mv;
     const int box_rows = page_size < FA_BN ? page_size : FA_BN;
@@ -973,9 +981,12 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
     if ((rc = make_map_2d(&mq, q, (uint64_t)num_tokens, (uint64_t)q_stride, (uint64_t)q_stride, FA_BM))) return rc;
     if ((rc = make_map_2d(&mk, k_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
     if ((rc = make_map_2d(&mv, v_cache, cache_rows, (uint64_t)head_dim, (uint64_t)head_dim, box_rows))) return rc;
-    if (mods) return head_dim == 64 ? launch_fa<64, true>(mq, mk, mv, p, work_tokens, work_rows, stream)
-                                    : launch_fa<128, true>(mq, mk, mv, p, work_tokens, work_rows, stream);
-    if (head_dim == 64) {
+#define FA_MODS(DD) (mods == 1 ? launch_fa<DD, 1>(mq, mk, mv, p, work_tokens, work_rows, stream)                                  \
+                     : mods == 2 ? launch_fa<DD, 2>(mq, mk, mv, p, work_tokens, work_rows, stream)                                \
+                                 : launch_fa<DD, 3>(mq, mk, mv, p, work_tokens, work_rows, stream))
+    if (mods) return head_dim == 64 ? FA_MODS(64) : FA_MODS(128);
+#undef FA_MODS
+    if (head_dim == 64 && !sink) {        // (the kernel with two query tiles side by side has no sink)
         // two query tiles side by side once there are three pairs for every SM (measured, 32 heads, one tile a block
         // against two side by side: 2,048 tokens 45.1 against 48.5 us, 4,096 tokens 143.7 against 142.4 us, 8,192 tokens
         // 496 against 462 us); below that the one-tile blocks, two on an SM, spread a launch over more SMs
@@ -983,9 +994,10 @@ extern "C" int mie_prefill_attention_tc(const void* q, int64_t q_stride, const v
         if ((tiles + 2 * work_rows) / 2 < 65535 &&
             (g_fa_pp_mode == 1 || (g_fa_pp_mode < 0 && tiles * num_heads >= 6 * (int64_t)device_sm_count())))
             return launch_fa_pp(mq, mk, mv, p, work_tokens, work_rows, stream);
-        return launch_fa<64, false>(mq, mk, mv, p, work_tokens, work_rows, stream);
+        return launch_fa<64, 0>(mq, mk, mv, p, work_tokens, work_rows, stream);
     }
-    return launch_fa<128, false>(mq, mk, mv, p, work_tokens, work_rows, stream);
+    if (head_dim == 64) return launch_fa<64, 0>(mq, mk, mv, p, work_tokens, work_rows, stream);
+    return launch_fa<128, 0>(mq, mk, mv, p, work_tokens, work_rows, stream);
 }
 
 // Which kernel serves head_dim 64: -1 chooses by the size of the launch (the default), 0 always one query tile a block,

@@ -30,7 +30,7 @@ __host__ __device__ __forceinline__ int mask_first_key(int pos, int window) {
 struct ScoreMods {
     float softcap;             // > 0: s <- softcap * tanh(s / softcap)
     const float* sink;         // not null, [heads]: exp(sink[head]) joins the softmax's denominator once (it has no key and no value)
-    const float* dist_bias;    // not null, [dist_len, heads]: the query at position p adds row min(p - j, dist_len - 1) to key j's score
+    const float* dist_bias;    // not null, [heads, dist_len]: the query at position p adds entry min(p - j, dist_len - 1) of its head's row to key j's score
     int dist_len;
 };
 // tanh as 1 - 2 / (exp(2x) + 1) with the fast exponential and division: absolute error about 1e-7, a handful of instructions
@@ -39,7 +39,7 @@ __device__ __forceinline__ float tanh_fast(float x) { return 1.0f - __fdividef(2
 template <bool FAST = false>
 __device__ __forceinline__ float mod_score(float s, const ScoreMods& m, int head, int num_heads, int dist) {
     if (m.softcap > 0.f) s = m.softcap * (FAST ? tanh_fast(s / m.softcap) : tanhf(s / m.softcap));
-    if (m.dist_bias) s += m.dist_bias[(int64_t)min(max(dist, 0), m.dist_len - 1) * num_heads + head];
+    if (m.dist_bias) s += m.dist_bias[head * m.dist_len + min(max(dist, 0), m.dist_len - 1)];
     return s;
 }
 

@@ -19,12 +19,20 @@
 
 #define MIE_K_LAYER_NORM 11
 
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(a, b);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+
 template <typename TO>
 __global__ void add_layernorm_kernel(float* __restrict__ res, float res_coef, const void* __restrict__ d0, int tag0, float c0,
                                      const void* __restrict__ d1, int tag1, float c1, const float* __restrict__ w,
                                      TO* __restrict__ out, const int* __restrict__ rows, int n, float eps, int center,
-                                     int num_in_rows, int* report) {
-    extern __shared__ float row_cache[];
+                                     int num_in_rows, int* report, int vec4) {
+    extern __shared__ __align__(16) float row_cache[];
     __shared__ float red[33];
     pdl_enter();
     const int b = blockIdx.x;
@@ -36,6 +44,23 @@ __global__ void add_layernorm_kernel(float* __restrict__ res, float res_coef, co
     float* res_row = res + r * n;
     const bool sums = d0 || d1 || res_coef != 1.0f;
     float s = 0.f;
+    if (vec4) {
+        // 16 bytes a load: rows of whole float4 (the caller has checked sizes, alignment and that the addends are float32)
+        const float4* r4 = reinterpret_cast<const float4*>(res_row);
+        const float4* a4 = d0 ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(d0) + r * n) : nullptr;
+        const float4* b4 = d1 ? reinterpret_cast<const float4*>(reinterpret_cast<const float*>(d1) + r * n) : nullptr;
+        for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+            float4 v = r4[i];
+            if (sums) {
+                v.x *= res_coef; v.y *= res_coef; v.z *= res_coef; v.w *= res_coef;
+                if (a4) { const float4 a = a4[i]; v.x = fmaf(c0, a.x, v.x); v.y = fmaf(c0, a.y, v.y); v.z = fmaf(c0, a.z, v.z); v.w = fmaf(c0, a.w, v.w); }
+                if (b4) { const float4 a = b4[i]; v.x = fmaf(c1, a.x, v.x); v.y = fmaf(c1, a.y, v.y); v.z = fmaf(c1, a.z, v.z); v.w = fmaf(c1, a.w, v.w); }
+                if (!rows) reinterpret_cast<float4*>(res_row)[i] = v;
+            }
+            reinterpret_cast<float4*>(row_cache)[i] = v;
+            s += (v.x + v.y) + (v.z + v.w);
+        }
+    } else
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v = res_row[i];
         if (sums) {
@@ -51,11 +76,20 @@ __global__ void add_layernorm_kernel(float* __restrict__ res, float res_coef, co
     if (center) {
         mean = block_sum(s, red) / (float)n;
         __syncthreads();                                           // `red` is used again below
+    } else {
+        __syncthreads();                                           // the row is read back by other threads than wrote it
     }
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) { const float dv = row_cache[i] - mean; ss += dv * dv; }
     const float rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)n + eps);
     TO* o_row = out + (int64_t)b * n;
+    if (vec4) {
+        for (int i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+            const float4 v = reinterpret_cast<const float4*>(row_cache)[i], ww = reinterpret_cast<const float4*>(w)[i];
+            store4(o_row + 4 * i, (v.x - mean) * rstd * ww.x, (v.y - mean) * rstd * ww.y, (v.z - mean) * rstd * ww.z, (v.w - mean) * rstd * ww.w);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < n; i += blockDim.x) o_row[i] = from_f32<TO>((row_cache[i] - mean) * rstd * w[i]);
 }
 
@@ -98,15 +132,18 @@ extern "C" int mie_add_layernorm(float* res, float res_coef, const void* d0, int
     if (smem > 200 * 1024) return MIE_ERR_TOO_LARGE;
     int threads = 32;
     while (threads < 512 && threads * 4 < n) threads <<= 1;
+    const auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const int vec4 = n % 4 == 0 && aligned(res) && aligned(w) && aligned(out) && (!d0 || (tag0 == MIE_F32 && aligned(d0))) &&
+                     (!d1 || (tag1 == MIE_F32 && aligned(d1)));
     cudaError_t e;
     if (act_tag == MIE_F32) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(add_layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
         return launch_kernel(add_layernorm_kernel<float>, dim3(num_rows), dim3(threads), smem, stream, res, res_coef, d0, tag0, c0, d1,
-                             tag1, c1, w, (float*)out, rows, n, eps, center, num_in_rows, g_range_report);
+                             tag1, c1, w, (float*)out, rows, n, eps, center, num_in_rows, g_range_report, vec4);
     } else if (act_tag == MIE_BF16) {
         if (smem > 48 * 1024 && (e = cudaFuncSetAttribute(add_layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess) return (int)e;
         return launch_kernel(add_layernorm_kernel<bf16>, dim3(num_rows), dim3(threads), smem, stream, res, res_coef, d0, tag0, c0, d1,
-                             tag1, c1, w, (bf16*)out, rows, n, eps, center, num_in_rows, g_range_report);
+                             tag1, c1, w, (bf16*)out, rows, n, eps, center, num_in_rows, g_range_report, vec4);
     }
     return MIE_ERR_BAD_ARG;
 }

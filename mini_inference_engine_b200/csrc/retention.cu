@@ -409,31 +409,51 @@ __global__ void gate_scan_kernel(const float* __restrict__ z, const float* __res
     float* ms = m_state + (int64_t)state_slots[r] * H + h;
     float m_c = *ms;
     const float b_i = bi ? bi[h] : 0.f, b_f = bf ? bf[h] : 0.f, inv = cap > 0.f ? 1.0f / cap : 0.f;
-    for (int t0 = 0; t0 < len; t0 += 32) {
-        const bool ok = t0 + lane < len;
-        const int64_t t = start + t0 + lane;
-        float gi = -INFINITY, f = 0.f;                         // lanes beyond the row: nothing is written, nothing forgotten
-        if (ok) {
-            float zi = z[t * 2 * H + h] + b_i, zf = z[t * 2 * H + H + h] + b_f;
-            if (cap > 0.f) { zi = cap * tanhf(zi * inv); zf = cap * tanhf(zf * inv); }
-            gi = zi;
-            f = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));     // log sigmoid
-        }
-        float L = f;
+    // four tiles' pre-activations are loaded before the first of them is scanned: the loads of a tile would otherwise stand
+    // in front of every tile's chain
+    for (int t00 = 0; t00 < len; t00 += 128) {
+        float zi4[4], zf4[4];
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const float up = __shfl_up_sync(0xffffffffu, L, o); if (lane >= o) L += up; }
-        float a = gi - L;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const float up = __shfl_up_sync(0xffffffffu, a, o); if (lane >= o) a = fmaxf(a, up); }
-        const float m = L + fmaxf(m_c, a);
-        float m_prev = __shfl_up_sync(0xffffffffu, m, 1);
-        if (lane == 0) m_prev = m_c;
-        if (ok) {
-            keep[t * H + h] = expf(f + m_prev - m);
-            write[t * H + h] = expf(gi - m);
-            m_out[t * H + h] = m;
+        for (int k = 0; k < 4; ++k) {
+            const int tt = t00 + 32 * k + lane;
+            const int64_t t = start + tt;
+            zi4[k] = tt < len ? z[t * 2 * H + h] : 0.f;
+            zf4[k] = tt < len ? z[t * 2 * H + H + h] : 0.f;
         }
-        m_c = __shfl_sync(0xffffffffu, m, min(31, len - t0 - 1));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int t0 = t00 + 32 * k;
+            if (t0 >= len) break;
+            const bool ok = t0 + lane < len;
+            const int64_t t = start + t0 + lane;
+            float gi = -INFINITY, f = 0.f;                         // lanes beyond the row: nothing is written, nothing forgotten
+            if (ok) {
+                float zi = zi4[k] + b_i, zf = zf4[k] + b_f;
+                if (cap > 0.f) { zi = cap * tanhf(zi * inv); zf = cap * tanhf(zf * inv); }
+                gi = zi;
+                f = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));     // log sigmoid
+            }
+            float L = f;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const float up = __shfl_up_sync(0xffffffffu, L, o); if (lane >= o) L += up; }
+            const float own = gi - L;
+            float a = own;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const float up = __shfl_up_sync(0xffffffffu, a, o); if (lane >= o) a = fmaxf(a, up); }
+            // u_j = m_j - L_j never falls, and f_j + m_{j-1} - m_j = u_{j-1} - u_j: where a token only forgets, its keep factor is
+            // exactly 1, and where it sets the maximum, its write factor is; no difference of large sums enters a factor that the
+            // state multiplies up over many tokens
+            const float u = fmaxf(m_c, a);
+            float u_prev = __shfl_up_sync(0xffffffffu, u, 1);
+            if (lane == 0) u_prev = m_c;
+            const float m = L + u;
+            if (ok) {
+                keep[t * H + h] = expf(u_prev - u);
+                write[t * H + h] = expf(own - u);
+                m_out[t * H + h] = m;
+            }
+            m_c = __shfl_sync(0xffffffffu, m, min(31, len - t0 - 1));
+        }
     }
     if (lane == 0) *ms = m_c;
 }

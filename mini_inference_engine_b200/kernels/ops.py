@@ -337,7 +337,8 @@ def rope_cache_write(qkv: torch.Tensor, positions, slots, cos, sin, k_cache, v_c
 
 class ScoreMods:
     """What an attention kernel does to a score between the scaled product and the softmax.  ``softcap`` c > 0: s <- c tanh(s / c).
-    ``dist_bias`` float32 [L, heads]: the query at position p adds row min(p - j, L - 1) to the score of key j (after the cap).
+    ``dist_bias`` float32 [heads, L]: the query at position p adds entry min(p - j, L - 1) of its head's row to the score of key j
+    (after the cap).
     ``sink`` float32 [heads]: exp(sink[head]) is one more term of the softmax's denominator, with no key and no value."""
 
     def __init__(self, softcap: float = 0.0, sink=None, dist_bias=None):
@@ -348,9 +349,9 @@ class ScoreMods:
             _need(self.sink.dtype == torch.float32 and self.sink.is_contiguous() and self.sink.numel() == num_heads, "one float32 sink per head")
         if self.dist_bias is not None:
             _need(self.dist_bias.dtype == torch.float32 and self.dist_bias.is_contiguous() and self.dist_bias.dim() == 2
-                  and self.dist_bias.shape[1] == num_heads and self.dist_bias.shape[0] >= 1, "distance bias must be float32 [L, heads]")
+                  and self.dist_bias.shape[0] == num_heads and self.dist_bias.shape[1] >= 1, "distance bias must be float32 [heads, L]")
         return (ctypes.c_float(self.softcap), _ptr(self.sink), _ptr(self.dist_bias),
-                int(self.dist_bias.shape[0]) if self.dist_bias is not None else 0)
+                int(self.dist_bias.shape[1]) if self.dist_bias is not None else 0)
 
 
 _NO_MODS = ScoreMods()

@@ -189,7 +189,7 @@ class GatedAttention(Mixer):
                 raise ValueError(f"a bias table of {rows} rows with a far distance of {far}")
             bucket = lambda n: n if n < half else min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
             idx = torch.tensor([bucket(n) for n in range(int(math.ceil(far)) + 1)], dtype=torch.long)
-            dist = tensors["rel"].float()[idx].to(rt.device).contiguous()             # [far + 1, H]
+            dist = tensors["rel"].float()[idx].t().to(rt.device).contiguous()         # [H, far + 1]: a head's biases side by side
         from ..kernels import ops
         self.mods = None
         if self.softcap > 0 or self.sink or dist is not None:

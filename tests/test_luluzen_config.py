@@ -122,9 +122,9 @@ def test_bias_table_by_distance_follows_the_bucket_rule():
         tensors["rel"] = torch.arange(rows, dtype=torch.float32)[:, None].expand(rows, 2).contiguous()
         part.bind(tensors, Runtime("cpu", torch.float32))
         table = part.mods.dist_bias
-        assert table.shape == (math.ceil(far) + 1, 2)
-        for n in range(table.shape[0] + 5):
-            assert table[min(n, table.shape[0] - 1), 0] == pz.distance_bucket(n, rows, far), (rows, far, n)
+        assert table.shape == (2, math.ceil(far) + 1)
+        for n in range(table.shape[1] + 5):
+            assert table[1, min(n, table.shape[1] - 1)] == pz.distance_bucket(n, rows, far), (rows, far, n)
 
 
 def test_preset_and_the_benchmark_pair_of_equal_size():
