@@ -37,7 +37,9 @@ struct PrefillParams {
     int modded;
 };
 
-template <int D>
+// MODS: the instance for scores that are modified before the softmax (a cap, a bias by distance: ScoreMods) and for a sink; the
+// plain instance tests nothing per score.
+template <int D, bool MODS>
 __global__ void __launch_bounds__(PRE_WARPS * 32)
 prefill_attention_kernel(const PrefillParams p) {
     constexpr int DP = D + 8;
@@ -93,7 +95,7 @@ prefill_attention_kernel(const PrefillParams p) {
 #pragma unroll
     for (int n = 0; n < NBLK; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    if (p.mods.sink) {                                              // the sink: one more term of every row's sum, with no value
+    if (MODS && p.mods.sink) {                                      // the sink: one more term of every row's sum, with no value
         m[0] = m[1] = p.mods.sink[head] * 1.4426950408889634f;
         l[0] = l[1] = 1.f;
     }
@@ -163,7 +165,7 @@ prefill_attention_kernel(const PrefillParams p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float v = s[n][i] * p.scale_log2e;
-                    if (p.modded)
+                    if (MODS && p.modded)
                         v = mod_score<true>(s[n][i] * p.scale, p.mods, head, p.num_heads, qpos[i >> 1] - (key0 + n * 8 + tq * 2 + (i & 1))) * 1.4426950408889634f;
                     if (need_mask) {
                         const int key = key0 + n * 8 + tq * 2 + (i & 1);
@@ -243,13 +245,18 @@ prefill_attention_kernel(const PrefillParams p) {
     }
 }
 
-template <int D>
-static int launch_prefill(const PrefillParams& p, int work_tokens, int work_rows, cudaStream_t stream) {
+template <int D, bool MODS>
+static int launch_prefill_as(const PrefillParams& p, int work_tokens, int work_rows, cudaStream_t stream) {
     const size_t smem = (size_t)2 * 2 * PRE_BN * (D + 8) * sizeof(bf16);
-    cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<D, MODS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     const dim3 grid((work_tokens + PRE_BM - 1) / PRE_BM + work_rows, p.num_heads);     // tiles <= tokens / 64 + rows
-    return launch_kernel(prefill_attention_kernel<D>, grid, dim3(PRE_WARPS * 32), smem, stream, p);
+    return launch_kernel(prefill_attention_kernel<D, MODS>, grid, dim3(PRE_WARPS * 32), smem, stream, p);
+}
+template <int D>
+static int launch_prefill(const PrefillParams& p, int work_tokens, int work_rows, cudaStream_t stream) {
+    return (p.modded || p.mods.sink) ? launch_prefill_as<D, true>(p, work_tokens, work_rows, stream)
+                                     : launch_prefill_as<D, false>(p, work_tokens, work_rows, stream);
 }
 
 // Rows with fewer than `min_q_len` new tokens are skipped (the decode kernel serves single tokens).  work_rows /
