@@ -29,7 +29,7 @@ __host__ __device__ __forceinline__ int mask_first_key(int pos, int window) {
 // What may happen to an attention score between the scaled product q . k and the softmax, each switched by its field:
 struct ScoreMods {
     float softcap;             // > 0: s <- softcap * tanh(s / softcap)
-    const float* sink;         // not null, [heads]: exp(sink[head]) joins the softmax's denominator once (it has no key and no value)
+    const float* sink;         // not null, [heads]: exp(sink[head]) is one more term of the softmax's denominator (a term without a score or a value of its own)
     const float* dist_bias;    // not null, [heads, dist_len]: the query at position p adds entry min(p - j, dist_len - 1) of its head's row to key j's score
     int dist_len;
 };

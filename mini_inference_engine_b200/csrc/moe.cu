@@ -315,7 +315,7 @@ __device__ __forceinline__ float expert_act(float x, int kind) {
 }
 
 // A gated expert's hidden value from its gate and up sums g, u and the token's weight w.  Kinds 0 - 2: w act(g) u.  Kind 3:
-// the weight multiplies the expert's INPUT (so both sums), and the gate is clamped: with g' = min(w g, limit),
+// the expert runs on the token times its weight (a factor on both sums), and the gate is clamped: with g' = min(w g, limit),
 // u' = clamp(w u, -limit, limit) the value is g' sigmoid(1.702 g') (u' + 1), and nothing multiplies the output.
 __device__ __forceinline__ float gated_value(float g, float u, float w, int kind, float limit) {
     if (kind != 3) return w * expert_act(g, kind) * u;

@@ -339,7 +339,7 @@ class ScoreMods:
     """What an attention kernel does to a score between the scaled product and the softmax.  ``softcap`` c > 0: s <- c tanh(s / c).
     ``dist_bias`` float32 [heads, L]: the query at position p adds entry min(p - j, L - 1) of its head's row to the score of key j
     (after the cap).
-    ``sink`` float32 [heads]: exp(sink[head]) is one more term of the softmax's denominator, with no key and no value."""
+    ``sink`` float32 [heads]: exp(sink[head]) is one more term of the softmax's denominator: a key that nothing scores and that carries no value."""
 
     def __init__(self, softcap: float = 0.0, sink=None, dist_bias=None):
         self.softcap, self.sink, self.dist_bias = float(softcap or 0.0), sink, dist_bias
@@ -1177,7 +1177,7 @@ def head_norm_gate(o: torch.Tensor, gate, weight, out: torch.Tensor, num_heads: 
 
 # --------------------------------------------------------------------------- routed experts
 
-# "clamped_in" (gated experts only): the token's weight multiplies the expert's input; with g = min(w gate, limit), u = clamp(w up,
+# "clamped_in" (gated experts only): the expert runs on the token scaled by its weight; with g = min(w gate, limit), u = clamp(w up,
 # -limit, limit) the hidden value is g sigmoid(1.702 g) (u + 1), and nothing multiplies the output
 EXPERT_ACTIVATIONS = {"relu2": 0, "silu": 1, "gelu_tanh": 2, "clamped_in": 3}
 

@@ -107,7 +107,7 @@ class GatedAttention(Mixer):
     * ``rel_bias`` (rows, far): a learned bias 'rel' [rows, heads] by distance n = p - j is added to the (scaled, capped) score:
       row n for n < rows / 2, else min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2)) (rows - rows/2)));
       ``rows`` None: the table's rows come from the checkpoint's tensor (a random model gets 32);
-    * ``sink``: a learned number per head ('sink') whose exponential joins the softmax's denominator, with no key or value.
+    * ``sink``: a learned number per head ('sink') whose exponential is one more term of the softmax's denominator (nothing is scored for it, nothing read).
 
     q, k, v and the gate are one product; norm, rotation, temperature and the cache write one kernel; attention
     itself is the framework's paged kernels (decode and portions); the gate one more."""

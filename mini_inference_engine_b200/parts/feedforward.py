@@ -164,7 +164,7 @@ class RoutedExperts(FeedForward):
         feed-forward that every token goes through ('shared.*'), added to the sum.  With identity experts or a shared one
         ``forward`` returns the outputs as ``Branches`` for the block's norm to sum."""
         # ``score`` "sigmoid": the ``top`` largest logits are chosen and each weight is the sigmoid of its own logit, not
-        # renormalized.  ``activation`` "clamped_in" (gated experts): the weight multiplies the expert's input instead of its
+        # renormalized.  ``activation`` "clamped_in" (gated experts): the expert runs on the token scaled by its weight, which then does not touch its
         # output, and the hidden value is g sigmoid(1.702 g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).
         outputs = num_experts + identity
         self.limit = float(limit or 0.0)

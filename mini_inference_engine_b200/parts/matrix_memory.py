@@ -5,7 +5,7 @@ computed per token and head, kept finite by a running maximum m of the log gates
     S_t = exp(f_t + m_{t-1} - m_t) S_{t-1} + exp(i_t - m_t) k_t v_t^T        n_t likewise with k_t alone
     o_t = S_t^T q_t / (max(|n_t . q_t|, exp(-m_t)) + 1e-6)                    q = W_q h dim^-1/2, k = W_k h, v = W_v h
 
-with S, n and m zero for a fresh request (m starts at 0, not at minus infinity).  Each head's o is divided by its root mean
+with S, n and m all zero for a fresh request (so the running maximum is never below the sum of the forget gates so far).  Each head's o is divided by its root mean
 square; the heads together are multiplied by the weight 'norm' and by sigmoid(W_g h) and projected by W_o.
 
 q|k|v|g are one product; the two gate rows per head are a second one that leaves float32.  The gates' chain runs token by
